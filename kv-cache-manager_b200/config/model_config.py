@@ -393,3 +393,117 @@ class BifatarConfig(ModelConfig):
     def to_json_dict(self) -> Dict[str, Any]:
         return {"architecture": self.architecture, "vocab": self.vocab, "width": self.width,
                 "norm": {"eps": self.norm_eps}, "layers": json.loads(json.dumps(list(self.layers)))}
+
+
+@dataclass(frozen=True)
+class RivetarConfig(ModelConfig):
+    """Rivetar: a decoder whose layers are listed one by one, every sublayer normalised on both sides
+    (x += norm_b(sublayer(norm(x))), the norms' weights stored as their distance from one), with a span of
+    layers that runs several times in a row.
+
+    Top level: ``vocab``, ``width``, ``norm.eps``, ``embedding.scale``, ``logit_softcap`` (optional, > 0),
+    ``loop`` {start, stop, times} (optional) and ``layers``: a list of {type, mixer, mlp}.
+    ``type`` "latent_attention": mixer {heads, dim, rot_dim, vdim, kv_rank, q_rank, scale, rot {base, dims}};
+    "attention": mixer {heads, kv_heads, dim, vdim, scale, rot {base, dims}, mask {size, keep_first} (optional)};
+    "gla": mixer {heads, dim, vdim, tau}.  ``mlp`` is null or {kind: "dense", ff}.
+    ``layers`` is kept as the parsed JSON after validation; the builder reads every size from it (the rank
+    of the decay's two-stage projection comes from the checkpoint's shapes, or from mixer key ``decay_rank``
+    when a model is made without a checkpoint)."""
+    vocab: int = 0
+    width: int = 0
+    norm_eps: float = 1e-6
+    embedding_scale: float = 1.0
+    logit_softcap: float = 0.0
+    loop_start: int = 0
+    loop_stop: int = 0
+    loop_times: int = 1
+    layers: tuple = ()
+
+    @classmethod
+    def from_json_dict(cls, d: Dict[str, Any]) -> "RivetarConfig":
+        w = "config.json (Rivetar)"
+        norm = _section(d, "norm", w)
+        emb = _section(d, "embedding", w, optional=True) or {}
+        loop = _section(d, "loop", w, optional=True)
+        layers = d.get("layers")
+        if not isinstance(layers, list) or not layers:
+            raise ConfigError(f"{w}: 'layers' must be a non-empty list")
+        cap = d.get("logit_softcap")
+        cfg = cls(architecture="Rivetar", vocab=_require(d, "vocab", int, w), width=_require(d, "width", int, w),
+                  norm_eps=_require(norm, "eps", float, w + " norm"),
+                  embedding_scale=_require(emb, "scale", float, w + " embedding") if "scale" in emb else 1.0,
+                  logit_softcap=_require(d, "logit_softcap", float, w) if cap is not None else 0.0,
+                  loop_start=_require(loop, "start", int, w + " loop") if loop else 0,
+                  loop_stop=_require(loop, "stop", int, w + " loop") if loop else 0,
+                  loop_times=_require(loop, "times", int, w + " loop") if loop else 1,
+                  layers=tuple(json.loads(json.dumps(layers))))
+        cfg.validate()
+        return cfg
+
+    @property
+    def has_loop(self) -> bool:
+        return self.loop_stop > self.loop_start
+
+    def validate(self) -> None:
+        w = "RivetarConfig"
+        if self.vocab <= 0 or self.width <= 0:
+            raise ConfigError(f"{w}: 'vocab' and 'width' must be positive")
+        if not (self.norm_eps > 0):
+            raise ConfigError(f"{w}: norm.eps must be positive, got {self.norm_eps}")
+        if self.logit_softcap < 0:
+            raise ConfigError(f"{w}: logit_softcap must be positive when given")
+        n = len(self.layers)
+        if self.loop_stop or self.loop_start or self.loop_times != 1:
+            if not (0 <= self.loop_start < self.loop_stop <= n) or self.loop_times < 1:
+                raise ConfigError(f"{w}: loop needs 0 <= start < stop <= {n} layers and times >= 1, got "
+                                  f"start {self.loop_start}, stop {self.loop_stop}, times {self.loop_times}")
+        for i, layer in enumerate(self.layers):
+            lw = f"{w}: layer {i}"
+            if not isinstance(layer, dict):
+                raise ConfigError(f"{lw} must be an object")
+            kind = layer.get("type")
+            m = _section(layer, "mixer", lw)
+            mw = lw + " mixer"
+            if kind == "latent_attention":
+                _positive_ints(m, ("heads", "dim", "rot_dim", "vdim", "kv_rank", "q_rank"), mw)
+                _require(m, "scale", float, mw)
+                rot = _section(m, "rot", mw)
+                dims = _require(rot, "dims", int, mw + " rot")
+                if _require(rot, "base", float, mw + " rot") <= 0 or dims <= 0 or dims % 2 or dims > m["rot_dim"]:
+                    raise ConfigError(f"{mw}: rot needs a positive base and an even 'dims' within 'rot_dim', got {rot!r}")
+            elif kind == "attention":
+                _check_heads(m, mw)
+                _require(m, "scale", float, mw)
+                _section(m, "rot", mw)
+                _check_rot(m, mw)
+                if m["vdim"] % 2:
+                    raise ConfigError(f"{mw}: values turn in pairs, 'vdim' must be even")
+                mask = _section(m, "mask", mw, optional=True)
+                if mask is not None:
+                    if _require(mask, "size", int, mw + " mask") <= 0:
+                        raise ConfigError(f"{mw}: mask.size must be positive")
+                    if mask.get("keep_first") is not None and _require(mask, "keep_first", int, mw + " mask") < 0:
+                        raise ConfigError(f"{mw}: mask.keep_first must not be negative")
+            elif kind == "gla":
+                _positive_ints(m, ("heads", "dim", "vdim"), mw)
+                if not (_require(m, "tau", float, mw) > 0):
+                    raise ConfigError(f"{mw}: tau must be positive")
+            else:
+                raise ConfigError(f"{lw}: unknown type {kind!r} (known: attention, gla, latent_attention)")
+            mlp = layer.get("mlp")
+            if mlp is None:
+                continue
+            if not isinstance(mlp, dict) or mlp.get("kind") != "dense":
+                raise ConfigError(f"{lw}: mlp must be null or of kind 'dense', got {mlp!r}")
+            if _require(mlp, "ff", int, lw + " mlp") <= 0:
+                raise ConfigError(f"{lw}: mlp.ff must be positive")
+
+    def to_json_dict(self) -> Dict[str, Any]:
+        d = {"architecture": self.architecture, "vocab": self.vocab, "width": self.width,
+             "norm": {"eps": self.norm_eps}, "embedding": {"scale": self.embedding_scale},
+             "layers": json.loads(json.dumps(list(self.layers)))}
+        if self.logit_softcap:
+            d["logit_softcap"] = self.logit_softcap
+        if self.has_loop:
+            d["loop"] = {"start": self.loop_start, "stop": self.loop_stop, "times": self.loop_times}
+        return d

@@ -32,6 +32,7 @@ struct DecodeParams {
   const int* seq_ctx_len;
   float* part_o; float* part_ml;
   int nh, nkv, block_size, window, part_size, num_parts;
+  int keep_first;                      // with a window: the first keep_first keys of a request stay visible to every row
   float scale_log2;                    // what a score is multiplied by on its way into exp2
   float cap_pre;                       // > 0: capped scores, s <- tanh(s * cap_pre) first (cap_pre = scale / cap, scale_log2 = cap * log2 e)
   const float* sink;                   // per head, or null: exp(sink) joins the denominator where the result is normalised
@@ -140,21 +141,26 @@ attn_decode_kernel(DecodeParams p) {
 
   const int ctx = p.seq_ctx_len[seq];
   const int lo = (p.window > 0 && ctx > p.window) ? ctx - p.window : 0;
-  const int begin = max(lo, part * p.part_size);
+  const int pbeg = part * p.part_size;
+  const int begin = max(lo, pbeg);
   const int end = min(ctx, (part + 1) * p.part_size);
+  // Kept first keys that lie below the window: [pbeg, kend) of this partition (kend <= lo <= begin).
+  const int kend = p.keep_first > 0 ? min(min(p.keep_first, lo), end) : 0;
+  const bool has_kept = kend > pbeg;
   float* mo = reinterpret_cast<float*>(kbuf);                       // [4][16][HD]   (after the key loop)
   float* mm = mo + 4 * 16 * HD;                                     // [4][16]
   float* mlsum = mm + 4 * 16;                                       // [4][16]
   float* bo = mlsum + 4 * 16;                                       // [16][HD] the block's result (cluster merge)
   float* bm = bo + 16 * HD;                                         // [16]
   float* bl = bm + 16;                                              // [16]
-  if (begin >= end) pdl_wait();
-  if (begin >= end && p.cluster_merge) {                           // nothing to read here, but the cluster waits
+  const bool nothing = begin >= end && !has_kept;
+  if (nothing) pdl_wait();
+  if (nothing && p.cluster_merge) {                           // nothing to read here, but the cluster waits
     if (tid < 16) { bm[tid] = -INFINITY; bl[tid] = 0.f; }
     cluster_merge_tail<HD>(p, seq, head0, heads_here, bo, bm, bl);
     return;
   }
-  if (begin >= end) {                                              // nothing to read here
+  if (nothing) {                                                   // nothing to read here
     for (int i = tid; i < heads_here * HD; i += kAttnThreads) {
       const int r = i / HD, d = i - r * HD;
       if (p.num_parts == 1) {
@@ -171,7 +177,8 @@ attn_decode_kernel(DecodeParams p) {
   // here instead of one inside every round of the key loop.
   const int* table = p.block_tables + size_t(seq) * p.max_blocks;
   {
-    const int first_page = begin / p.block_size, n_pages = (end - 1) / p.block_size - first_page + 1;
+    const int first_page = (has_kept ? pbeg : begin) / p.block_size;
+    const int n_pages = ((begin < end ? end : kend) - 1) / p.block_size - first_page + 1;
     if (n_pages <= kTabMax) {
       for (int j = tid; j < n_pages; j += kAttnThreads) stab[j] = table[first_page + j];
       table = stab - first_page;
@@ -179,13 +186,20 @@ attn_decode_kernel(DecodeParams p) {
     }
   }
 
+  // Tiles: those of the kept first keys that start below the window's first tile, then the window's.
   const int t_first = (begin / kKeyTile) * kKeyTile;
-  const int n_tiles = (end - t_first + kKeyTile - 1) / kKeyTile;
+  const int n_win = begin < end ? (end - t_first + kKeyTile - 1) / kKeyTile : 0;
+  int n_kept = has_kept ? (kend - pbeg + kKeyTile - 1) / kKeyTile : 0;
+  if (n_win > 0) n_kept = min(n_kept, (t_first - pbeg) / kKeyTile);
+  const int n_tiles = n_kept + n_win;
+  const int load_lo = has_kept ? pbeg : begin;
+  auto tile_start = [&](int i) { return i < n_kept ? pbeg + i * kKeyTile : t_first + (i - n_kept) * kKeyTile; };
   auto load_stage = [&](int i) {                                   // tile i -> ring slot i % stages
     const int sl = i % kKVStages;
     if (i < n_tiles) {
       load_kv_tiles<HD>(kbuf + sl * kKeyTile * LD, vbuf + sl * kKeyTile * LD, p.k_cache, p.v_cache, table,
-                        t_first + i * kKeyTile, begin, end, kvh, p.nkv, p.block_size, tid, kAttnThreads, p.log2_block);
+                        tile_start(i), load_lo, i < n_kept ? kend : end, kvh, p.nkv, p.block_size, tid, kAttnThreads,
+                        p.log2_block);
     }
     cp_async_commit();                                             // one group per tile, empty ones too
   };
@@ -193,7 +207,7 @@ attn_decode_kernel(DecodeParams p) {
   // this one) are requested before the wait; the rest of the first stages after it.
   int ahead = 0;
   for (; ahead < kKVStages - 1; ++ahead) {
-    if (t_first + (ahead + 1) * kKeyTile > ctx - 1) break;
+    if (ahead >= n_tiles || tile_start(ahead) + kKeyTile > ctx - 1) break;
     load_stage(ahead);
   }
   pdl_wait();
@@ -224,12 +238,12 @@ attn_decode_kernel(DecodeParams p) {
   };
   int slot = 0;                                                    // ring slot of tile i (counted along: i % stages)
   for (int i = 0; i < n_tiles; ++i) {
-    const int t0 = t_first + i * kKeyTile;
+    const int t0 = tile_start(i);
     load_stage(i + kKVStages - 1);                                 // its slot was freed by the barrier that
     cp_async_wait<kKVStages - 1>();                                // ended round i - 1; tile i has landed
     round_barrier();
     const int kb = t0 + warp * 16;                                 // this warp's 16 keys
-    if (kb < end && kb + 16 > begin) {
+    if ((kb < end && kb + 16 > begin) || (has_kept && kb < kend)) {
       const bf16* kt = kbuf + slot * kKeyTile * LD + warp * 16 * LD;
       const bf16* vt = vbuf + slot * kKeyTile * LD + warp * 16 * LD;
       float s[2][4];
@@ -250,7 +264,7 @@ attn_decode_kernel(DecodeParams p) {
           mma_bf16(s[1], a, b[2], b[3]);
         }
       }
-      if (kb >= begin && kb + 16 <= end) {                         // all sixteen keys count: no masks
+      if ((kb >= begin && kb + 16 <= end) || (has_kept && kb + 16 <= kend)) {   // all sixteen keys count: no masks
 #pragma unroll
         for (int h = 0; h < 2; ++h)
 #pragma unroll
@@ -262,7 +276,7 @@ attn_decode_kernel(DecodeParams p) {
           for (int j = 0; j < 4; ++j) {
             const int key = kb + 8 * h + 2 * t4 + (j & 1);
             const float capped = (p.cap_pre > 0.f ? fast_tanh(s[h][j] * p.cap_pre) : s[h][j]) * p.scale_log2;
-            s[h][j] = (key >= begin && key < end) ? capped : -INFINITY;
+            s[h][j] = ((key >= begin && key < end) || (has_kept && key < kend)) ? capped : -INFINITY;
           }
       }
       uint32_t pa[4];
@@ -451,12 +465,13 @@ KVCM_API int kvcm_attention_decode_cluster_parts(void) { return kMaxClusterParts
 // merge runs inside a cluster (cluster_merge != 0 and num_parts <= kvcm_attention_decode_cluster_parts()).
 // `softcap` > 0: scaled scores are capped as cap * tanh(score / cap); `sink` (per head, optional): exp(sink)
 // joins the softmax's denominator.
-KVCM_API int kvcm_attention_decode_capped_bf16(const void* q, int q_stride, void* out, int out_stride,
-                                               const void* k_cache, const void* v_cache, const int* block_tables,
-                                               int max_blocks, const int* seq_ctx_len, int seqs, int nh, int nkv,
-                                               int hd, int block_size, float scale, int window, int part_size,
-                                               int num_parts, float* scratch, int cluster_merge, float softcap,
-                                               const float* sink, void* stream) {
+// `keep_first` > 0 (with a window): the first keep_first keys of every request stay visible.
+KVCM_API int kvcm_attention_decode_keep_bf16(const void* q, int q_stride, void* out, int out_stride,
+                                             const void* k_cache, const void* v_cache, const int* block_tables,
+                                             int max_blocks, const int* seq_ctx_len, int seqs, int nh, int nkv,
+                                             int hd, int block_size, float scale, int window, int keep_first, int part_size,
+                                             int num_parts, float* scratch, int cluster_merge, float softcap,
+                                             const float* sink, void* stream) {
   if (seqs == 0) return 0;
   static int sm_count = 0;
   if (sm_count == 0) {
@@ -474,6 +489,7 @@ KVCM_API int kvcm_attention_decode_capped_bf16(const void* q, int q_stride, void
   p.block_tables = block_tables; p.max_blocks = max_blocks; p.seq_ctx_len = seq_ctx_len;
   p.part_o = scratch; p.part_ml = scratch ? scratch + (size_t)seqs * nh * num_parts * hd : nullptr;
   p.nh = nh; p.nkv = nkv; p.block_size = block_size; p.window = window;
+  p.keep_first = window > 0 && keep_first > 0 ? keep_first : 0;
   p.part_size = part_size; p.num_parts = num_parts; p.cluster_merge = cluster_merge;
   p.scale_log2 = (softcap > 0.f ? softcap : scale) * 1.4426950408889634f;
   p.cap_pre = softcap > 0.f ? scale / softcap : 0.f;
@@ -487,6 +503,17 @@ KVCM_API int kvcm_attention_decode_capped_bf16(const void* q, int q_stride, void
   if (rc != 0 || num_parts == 1 || cluster_merge) return rc;
   return pdl_launch(attn_decode_merge_kernel, dim3(seqs, nh), dim3(hd < 64 ? 32 : 64), 0, (cudaStream_t)stream,
                     (const float*)p.part_o, (const float*)p.part_ml, p.out, out_stride, nh, hd, num_parts, p.sink);
+}
+
+KVCM_API int kvcm_attention_decode_capped_bf16(const void* q, int q_stride, void* out, int out_stride,
+                                               const void* k_cache, const void* v_cache, const int* block_tables,
+                                               int max_blocks, const int* seq_ctx_len, int seqs, int nh, int nkv,
+                                               int hd, int block_size, float scale, int window, int part_size,
+                                               int num_parts, float* scratch, int cluster_merge, float softcap,
+                                               const float* sink, void* stream) {
+  return kvcm_attention_decode_keep_bf16(q, q_stride, out, out_stride, k_cache, v_cache, block_tables, max_blocks, seq_ctx_len,
+                                         seqs, nh, nkv, hd, block_size, scale, window, 0, part_size, num_parts, scratch,
+                                         cluster_merge, softcap, sink, stream);
 }
 
 KVCM_API int kvcm_attention_decode_bf16(const void* q, int q_stride, void* out, int out_stride,

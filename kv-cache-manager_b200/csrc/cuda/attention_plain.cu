@@ -10,6 +10,8 @@
 //
 // Arithmetic as the reference's kernel (src/cuda/paged_attention.cu:80-182): q is scaled first,
 // the causal mask is the loop bound ctx = position + 1, o = (sum_t p_t v_t) / sum_t p_t.
+// With a window, `keep_first` > 0 keeps the first keep_first keys of the request visible to every row: the
+// keys walked are [0, min(keep_first, lo)) followed by the window [lo, ctx).
 #include "common.cuh"
 
 namespace kvcm {
@@ -25,7 +27,7 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
                        const int* __restrict__ block_tables, int max_blocks,
                        const int* __restrict__ row_seq, const int* __restrict__ positions,
                        int nh, int nkv, int hd, int block_size, float scale, int window, float softcap,
-                       const float* __restrict__ sink) {
+                       const float* __restrict__ sink, int keep_first) {
   extern __shared__ float smem[];
   float* qs = smem;                     // [hd]
   float* sc = qs + hd;                  // [kPlainChunk]
@@ -34,6 +36,8 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
   const int kvh = h / (nh / nkv);
   const int ctx = positions[row] + 1;
   const int lo = (window > 0 && ctx > window) ? ctx - window : 0;
+  const int kept = min(keep_first, lo);          // keys [0, kept) come first, then [lo, ctx)
+  const int total = kept + ctx - lo;
   const int* table = block_tables + size_t(row_seq[row]) * max_blocks;
   const size_t head_stride = size_t(block_size) * hd;
   const size_t page_stride = head_stride * nkv;
@@ -46,11 +50,11 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
   const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
   float acc[kPlainMaxDimsPerThread] = {0.f, 0.f, 0.f, 0.f};
 
-  for (int c0 = lo; c0 < ctx; c0 += kPlainChunk) {
-    const int n = min(kPlainChunk, ctx - c0);
+  for (int c0 = 0; c0 < total; c0 += kPlainChunk) {
+    const int n = min(kPlainChunk, total - c0);
     float local_max = -INFINITY;
     for (int j = tid; j < n; j += kPlainThreads) {
-      const int t = c0 + j;
+      const int t = c0 + j < kept ? c0 + j : c0 + j - kept + lo;
       const int page = table[t / block_size];
       const T* kp = k_cache + size_t(page) * page_stride + size_t(kvh) * head_stride +
                     size_t(t % block_size) * hd;
@@ -76,7 +80,7 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
       if (d >= hd) break;
       float a = acc[i] * factor;
       for (int j = 0; j < n; ++j) {
-        const int t = c0 + j;
+        const int t = c0 + j < kept ? c0 + j : c0 + j - kept + lo;
         const int page = table[t / block_size];
         a = fmaf(sc[j], ldf(v_cache + size_t(page) * page_stride + size_t(kvh) * head_stride +
                             size_t(t % block_size) * hd + d), a);
@@ -96,14 +100,15 @@ template <typename T>
 int launch_attention_plain(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
                            const void* v_cache, const int* block_tables, int max_blocks,
                            const int* row_seq, const int* positions, int rows, int nh, int nkv, int hd,
-                           int block_size, float scale, int window, float softcap, const float* sink, cudaStream_t s) {
+                           int block_size, float scale, int window, float softcap, const float* sink, int keep_first, cudaStream_t s) {
   if (rows == 0) return 0;
   if (hd > kPlainMaxDimsPerThread * kPlainThreads || nkv <= 0 || nh % nkv) return KVCM_ERR_UNSUPPORTED;
   const size_t smem = (size_t(hd) + kPlainChunk + 33) * sizeof(float);
   dim3 grid(rows, nh);
   attention_plain_kernel<T><<<grid, kPlainThreads, smem, s>>>(
       (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_cache, (const T*)v_cache, block_tables,
-      max_blocks, row_seq, positions, nh, nkv, hd, block_size, scale, window, softcap, sink);
+      max_blocks, row_seq, positions, nh, nkv, hd, block_size, scale, window, softcap, sink,
+      window > 0 && keep_first > 0 ? keep_first : 0);
   return KVCM_LAUNCH_RESULT();
 }
 
@@ -111,21 +116,26 @@ int launch_attention_plain(const void* q, int q_stride, void* out, int out_strid
 
 using namespace kvcm;
 
-KVCM_API int kvcm_attention_plain_f32(const void* q, int q_stride, void* out, int out_stride,
-                                      const void* k_cache, const void* v_cache, const int* block_tables,
-                                      int max_blocks, const int* row_seq, const int* positions, int rows,
-                                      int nh, int nkv, int hd, int block_size, float scale, int window,
-                                      float softcap, const float* sink, void* stream) {
-  return launch_attention_plain<float>(q, q_stride, out, out_stride, k_cache, v_cache, block_tables,
-                                       max_blocks, row_seq, positions, rows, nh, nkv, hd, block_size,
-                                       scale, window, softcap, sink, (cudaStream_t)stream);
+#define KVCM_PLAIN_ARGS                                                                                              \
+  const void *q, int q_stride, void *out, int out_stride, const void *k_cache, const void *v_cache,                  \
+      const int *block_tables, int max_blocks, const int *row_seq, const int *positions, int rows, int nh, int nkv, \
+      int hd, int block_size, float scale, int window, float softcap, const float *sink
+
+KVCM_API int kvcm_attention_plain_keep_f32(KVCM_PLAIN_ARGS, int keep_first, void* stream) {
+  return launch_attention_plain<float>(q, q_stride, out, out_stride, k_cache, v_cache, block_tables, max_blocks, row_seq,
+                                       positions, rows, nh, nkv, hd, block_size, scale, window, softcap, sink, keep_first,
+                                       (cudaStream_t)stream);
 }
-KVCM_API int kvcm_attention_plain_bf16(const void* q, int q_stride, void* out, int out_stride,
-                                       const void* k_cache, const void* v_cache, const int* block_tables,
-                                       int max_blocks, const int* row_seq, const int* positions, int rows,
-                                       int nh, int nkv, int hd, int block_size, float scale, int window,
-                                       float softcap, const float* sink, void* stream) {
-  return launch_attention_plain<bf16>(q, q_stride, out, out_stride, k_cache, v_cache, block_tables,
-                                      max_blocks, row_seq, positions, rows, nh, nkv, hd, block_size,
-                                      scale, window, softcap, sink, (cudaStream_t)stream);
+KVCM_API int kvcm_attention_plain_keep_bf16(KVCM_PLAIN_ARGS, int keep_first, void* stream) {
+  return launch_attention_plain<bf16>(q, q_stride, out, out_stride, k_cache, v_cache, block_tables, max_blocks, row_seq,
+                                      positions, rows, nh, nkv, hd, block_size, scale, window, softcap, sink, keep_first,
+                                      (cudaStream_t)stream);
+}
+KVCM_API int kvcm_attention_plain_f32(KVCM_PLAIN_ARGS, void* stream) {
+  return kvcm_attention_plain_keep_f32(q, q_stride, out, out_stride, k_cache, v_cache, block_tables, max_blocks, row_seq,
+                                       positions, rows, nh, nkv, hd, block_size, scale, window, softcap, sink, 0, stream);
+}
+KVCM_API int kvcm_attention_plain_bf16(KVCM_PLAIN_ARGS, void* stream) {
+  return kvcm_attention_plain_keep_bf16(q, q_stride, out, out_stride, k_cache, v_cache, block_tables, max_blocks, row_seq,
+                                        positions, rows, nh, nkv, hd, block_size, scale, window, softcap, sink, 0, stream);
 }

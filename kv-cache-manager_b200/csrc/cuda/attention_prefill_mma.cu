@@ -20,6 +20,7 @@ struct PrefillParams {
   const int* tile_seq; const int* tile_q0;
   const int* seq_q_start; const int* seq_q_len; const int* seq_ctx_len;
   int nh, nkv, block_size, window;
+  int keep_first;                   // with a window: the first keep_first keys of a request stay visible to every row
   float scale_log2;                 // what a score is multiplied by on its way into exp2
   float cap_pre;                    // > 0: capped scores, s <- tanh(s * cap_pre) first (cap_pre = scale / cap, scale_log2 = cap * log2 e)
   const float* sink;                // per head, or null: exp(sink) joins every row's denominator at the end
@@ -58,10 +59,15 @@ attn_prefill_kernel(PrefillParams p) {
       v = *reinterpret_cast<const uint4*>(p.q + size_t(q_start + q0 + r) * p.q_stride + size_t(head) * HD + ch * 8);
     *reinterpret_cast<uint4*>(qtile + r * LD + ch * 8) = v;
   }
+  // Tiles: those of the kept first keys that start below the window's first tile, then the window's.
   const int t_first = (lo / kKeyTile) * kKeyTile;
-  const int n_tiles = (hi - t_first + kKeyTile - 1) / kKeyTile;
-  load_kv_tiles<HD>(kbuf, vbuf, p.k_cache, p.v_cache, table, t_first, lo, hi, kvh, p.nkv, p.block_size, tid,
-                    kAttnThreads, p.log2_block);
+  const int kend = p.keep_first > 0 ? min(p.keep_first, lo) : 0;    // kept keys below the tile's window: [0, kend)
+  const int n_kept = min((kend + kKeyTile - 1) / kKeyTile, t_first / kKeyTile);
+  const int n_tiles = n_kept + (hi - t_first + kKeyTile - 1) / kKeyTile;
+  const int load_lo = kend > 0 ? 0 : lo;
+  auto tile_start = [&](int i) { return i < n_kept ? i * kKeyTile : t_first + (i - n_kept) * kKeyTile; };
+  load_kv_tiles<HD>(kbuf, vbuf, p.k_cache, p.v_cache, table, tile_start(0), load_lo, n_kept > 0 ? kend : hi, kvh, p.nkv,
+                    p.block_size, tid, kAttnThreads, p.log2_block);
   cp_async_commit();
   __syncthreads();
 
@@ -80,18 +86,19 @@ attn_prefill_kernel(PrefillParams p) {
   for (int d = 0; d < HD / 8; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
 
   for (int i = 0; i < n_tiles; ++i) {
-    const int t0 = t_first + i * kKeyTile;
+    const int t0 = tile_start(i);
     if (i + 1 < n_tiles) {
       const int nb = (i + 1) & 1;
       load_kv_tiles<HD>(kbuf + nb * kKeyTile * LD, vbuf + nb * kKeyTile * LD, p.k_cache, p.v_cache, table,
-                        t0 + kKeyTile, lo, hi, kvh, p.nkv, p.block_size, tid, kAttnThreads, p.log2_block);
+                        tile_start(i + 1), load_lo, i + 1 < n_kept ? kend : hi, kvh, p.nkv, p.block_size, tid, kAttnThreads,
+                        p.log2_block);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
       cp_async_wait<0>();
     }
     __syncthreads();
-    if (warp_live && t0 <= warp_last_pos && t0 + kKeyTile > max(lo, warp_first_lo)) {
+    if (warp_live && t0 <= warp_last_pos && (t0 + kKeyTile > max(lo, warp_first_lo) || t0 < p.keep_first)) {
       const bf16* kt = kbuf + (i & 1) * kKeyTile * LD;
       const bf16* vt = vbuf + (i & 1) * kKeyTile * LD;
       // scores of this warp's 16 rows against the tile's 64 keys: s[2*sub], s[2*sub+1] = keys of sub-block sub
@@ -117,7 +124,7 @@ attn_prefill_kernel(PrefillParams p) {
         }
       }
       // scale; mask only where the tile touches the diagonal, the window's edge or the key range's edge
-      const bool needs_mask = t0 + kKeyTile - 1 > pos0 + warp * 16 || t0 < lo ||
+      const bool needs_mask = t0 + kKeyTile - 1 > pos0 + warp * 16 || t0 < lo || p.keep_first > 0 ||
                               (p.window > 0 && t0 <= warp_last_pos - p.window) || t0 + kKeyTile > hi;
       float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -128,7 +135,7 @@ attn_prefill_kernel(PrefillParams p) {
           if (needs_mask) {
             const int key = t0 + 8 * n + 2 * t4 + (j & 1);
             const int rp = row_pos[j >> 1];
-            const bool ok = key <= rp && key >= lo && key < hi && (p.window <= 0 || key > rp - p.window);
+            const bool ok = key <= rp && key < hi && ((key >= lo && (p.window <= 0 || key > rp - p.window)) || key < p.keep_first);
             v = ok ? v : -INFINITY;
           }
           s[n][j] = v;
@@ -210,12 +217,13 @@ int launch_prefill(const PrefillParams& p, int tiles, cudaStream_t s) {
 
 using namespace kvcm;
 
-KVCM_API int kvcm_attention_prefill_bf16(const void* q, int q_stride, void* out, int out_stride,
-                                         const void* k_cache, const void* v_cache, const int* block_tables,
-                                         int max_blocks, const int* tile_seq, const int* tile_q0,
-                                         const int* seq_q_start, const int* seq_q_len, const int* seq_ctx_len,
-                                         int tiles, int nh, int nkv, int hd, int block_size, float scale,
-                                         int window, float softcap, const float* sink, void* stream) {
+// `keep_first` > 0 (with a window): the first keep_first keys of every request stay visible.
+KVCM_API int kvcm_attention_prefill_keep_bf16(const void* q, int q_stride, void* out, int out_stride,
+                                              const void* k_cache, const void* v_cache, const int* block_tables,
+                                              int max_blocks, const int* tile_seq, const int* tile_q0,
+                                              const int* seq_q_start, const int* seq_q_len, const int* seq_ctx_len,
+                                              int tiles, int nh, int nkv, int hd, int block_size, float scale,
+                                              int window, int keep_first, float softcap, const float* sink, void* stream) {
   if (tiles == 0) return 0;
   if (nkv <= 0 || nh % nkv) return KVCM_ERR_UNSUPPORTED;
   PrefillParams p;
@@ -224,6 +232,7 @@ KVCM_API int kvcm_attention_prefill_bf16(const void* q, int q_stride, void* out,
   p.block_tables = block_tables; p.max_blocks = max_blocks; p.tile_seq = tile_seq; p.tile_q0 = tile_q0;
   p.seq_q_start = seq_q_start; p.seq_q_len = seq_q_len; p.seq_ctx_len = seq_ctx_len;
   p.nh = nh; p.nkv = nkv; p.block_size = block_size; p.window = window;
+  p.keep_first = window > 0 && keep_first > 0 ? keep_first : 0;
   p.scale_log2 = (softcap > 0.f ? softcap : scale) * 1.4426950408889634f;
   p.cap_pre = softcap > 0.f ? scale / softcap : 0.f;
   p.sink = sink;
@@ -234,4 +243,15 @@ KVCM_API int kvcm_attention_prefill_bf16(const void* q, int q_stride, void* out,
   KVCM_FOR_HEAD_DIMS(X)
 #undef X
   return rc;
+}
+
+KVCM_API int kvcm_attention_prefill_bf16(const void* q, int q_stride, void* out, int out_stride,
+                                         const void* k_cache, const void* v_cache, const int* block_tables,
+                                         int max_blocks, const int* tile_seq, const int* tile_q0,
+                                         const int* seq_q_start, const int* seq_q_len, const int* seq_ctx_len,
+                                         int tiles, int nh, int nkv, int hd, int block_size, float scale,
+                                         int window, float softcap, const float* sink, void* stream) {
+  return kvcm_attention_prefill_keep_bf16(q, q_stride, out, out_stride, k_cache, v_cache, block_tables, max_blocks, tile_seq,
+                                          tile_q0, seq_q_start, seq_q_len, seq_ctx_len, tiles, nh, nkv, hd, block_size, scale,
+                                          window, 0, softcap, sink, stream);
 }

@@ -6,10 +6,14 @@
 //   2. norm over the WHOLE q projection and over the whole k projection (optional):
 //        q <- wq * q / sqrt(mean(q^2) + eps),  k likewise with wk
 //   3. rotation of the first `rot` dimensions of every q and k head in rotate-half pairs
-//        (i, i + rot/2), angle = position * inv_freq[i]   (rot == 0: none)
+//        (i, i + rot/2), or with `interleaved` in neighbouring pairs (2i, 2i + 1),
+//        angle = position * inv_freq[i]   (rot == 0: none)
 //   4. norm per head, without weights (optional):  x <- x / sqrt(mean_head(x^2) + eps)
 //   5. values: `v_keep` (optional, float [rows, nkv*dv]) receives v as projected;
-//        `v_first` (optional, the same layout) mixes:  v <- v + lambda (v_first - v), evaluated as (1 - lambda) v + lambda v_first
+//        `v_first` (optional, the same layout) mixes:  v <- v + lambda (v_first - v), evaluated as (1 - lambda) v + lambda v_first;
+//        `v_inv_freq` (optional, dv/2 frequencies) turns every value head by its own position over all dv
+//        dimensions, in the same pairing as q and k (what is cached is the turned value; the reader turns
+//        the attention's output back by its own position)
 //   6. q goes to q_out [rows, nh*HD] in the storage type, k and v to the row's page slot
 //        [pages, nkv, page, HD]; HD >= max(dk, dv), elements beyond a head's own size are zero
 //        (zeros add nothing to a score, and the attention output's columns beyond dv stay zero).
@@ -32,6 +36,8 @@ struct AttnPrepareParams {
   const int* slot_mapping; int block_size;
   void* q_out; void* k_cache; void* v_cache;
   int nh, nkv, dk, dv, HD;
+  int interleaved;                   // pairs (2i, 2i+1) instead of (i, i + half)
+  const float* v_inv_freq;           // [dv/2] or null
 };
 
 __device__ __forceinline__ void store_pair(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
@@ -51,10 +57,13 @@ attn_prepare_kernel(AttnPrepareParams p) {
   const int n = nq + nk + nv;
   const int half = p.rot / 2;
   float* cs_table = row + n;
+  float* vcs_table = cs_table + p.rot;               // dv floats: cosines, sines of the values' turn
+  const int vhalf = p.v_inv_freq ? p.dv / 2 : 0;
   // the row's cosines and sines depend on nothing the step computes: before the wait
-  if (half > 0) {
+  if (half > 0 || vhalf > 0) {
     const float pos = float(p.positions[r]);
     for (int j = tid; j < half; j += blockDim.x) sincosf(pos * p.inv_freq[j], &cs_table[half + j], &cs_table[j]);
+    for (int j = tid; j < vhalf; j += blockDim.x) sincosf(pos * p.v_inv_freq[j], &vcs_table[vhalf + j], &vcs_table[j]);
   }
   pdl_wait();
   const float* src = p.proj + size_t(r) * p.ldp;
@@ -96,10 +105,11 @@ attn_prepare_kernel(AttnPrepareParams p) {
         __syncwarp();
       }
       for (int j = lane; j < half; j += 32) {
+        const int ia = p.interleaved ? 2 * j : j, ib = p.interleaved ? 2 * j + 1 : j + half;
         float a, b;
-        rotate_pair(x[j], x[j + half], cs_table[j], cs_table[half + j], a, b);
-        x[j] = a;
-        x[j + half] = b;
+        rotate_pair(x[ia], x[ib], cs_table[j], cs_table[half + j], a, b);
+        x[ia] = a;
+        x[ib] = b;
       }
       __syncwarp();
       float inv = 1.f;
@@ -128,6 +138,16 @@ attn_prepare_kernel(AttnPrepareParams p) {
         __syncwarp();
       }
       if (slot < 0) continue;
+      if (vhalf > 0) {
+        for (int j = lane; j < vhalf; j += 32) {
+          const int ia = p.interleaved ? 2 * j : j, ib = p.interleaved ? 2 * j + 1 : j + vhalf;
+          float a, b;
+          rotate_pair(x[ia], x[ib], vcs_table[j], vcs_table[vhalf + j], a, b);
+          x[ia] = a;
+          x[ib] = b;
+        }
+        __syncwarp();
+      }
       T* dst = reinterpret_cast<T*>(p.v_cache) + base + head * head_stride;
       for (int d = 2 * lane; d < p.HD; d += 64) store_pair(dst + d, d < p.dv ? x[d] : 0.f, d + 1 < p.dv ? x[d + 1] : 0.f);
     }
@@ -137,8 +157,8 @@ attn_prepare_kernel(AttnPrepareParams p) {
 template <typename T>
 int launch_attn_prepare(const AttnPrepareParams& p, int rows, cudaStream_t s) {
   if (rows == 0) return 0;
-  if (p.rot % 2 || p.rot > p.dk || p.HD < p.dk || p.HD < p.dv || p.HD % 2) return KVCM_ERR_UNSUPPORTED;
-  const size_t smem = size_t(p.nh * p.dk + p.nkv * p.dk + p.nkv * p.dv + p.rot) * sizeof(float);
+  if (p.rot % 2 || p.rot > p.dk || p.HD < p.dk || p.HD < p.dv || p.HD % 2 || (p.v_inv_freq && p.dv % 2)) return KVCM_ERR_UNSUPPORTED;
+  const size_t smem = size_t(p.nh * p.dk + p.nkv * p.dk + p.nkv * p.dv + p.rot + (p.v_inv_freq ? p.dv : 0)) * sizeof(float);
   if (smem > 200 * 1024) return KVCM_ERR_UNSUPPORTED;
   if (smem > 48 * 1024) {
     const cudaError_t e = cudaFuncSetAttribute(attn_prepare_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
@@ -157,7 +177,7 @@ using namespace kvcm;
   const float *proj, int ldp, const float *bias, const float *wq, const float *wk, const int *positions,              \
       const float *inv_freq, int rot, int head_norm, float eps, float *v_keep, const float *v_first,                  \
       const float *lambda, const int *slot_mapping, int block_size, void *q_out, void *k_cache, void *v_cache,        \
-      int rows, int nh, int nkv, int dk, int dv, int HD, void *stream
+      int rows, int nh, int nkv, int dk, int dv, int HD, int interleaved, const float *v_inv_freq, void *stream
 
 static AttnPrepareParams make_params(KVCM_ATTN_PREPARE_ARGS) {
   (void)rows; (void)stream;
@@ -165,17 +185,17 @@ static AttnPrepareParams make_params(KVCM_ATTN_PREPARE_ARGS) {
   p.proj = proj; p.ldp = ldp; p.bias = bias; p.wq = wq; p.wk = wk; p.positions = positions; p.inv_freq = inv_freq;
   p.rot = inv_freq ? rot : 0; p.head_norm = head_norm; p.eps = eps; p.v_keep = v_keep; p.v_first = v_first; p.lambda = lambda;
   p.slot_mapping = slot_mapping; p.block_size = block_size; p.q_out = q_out; p.k_cache = k_cache; p.v_cache = v_cache;
-  p.nh = nh; p.nkv = nkv; p.dk = dk; p.dv = dv; p.HD = HD;
+  p.nh = nh; p.nkv = nkv; p.dk = dk; p.dv = dv; p.HD = HD; p.interleaved = interleaved; p.v_inv_freq = v_inv_freq;
   return p;
 }
 
 KVCM_API int kvcm_attn_prepare_f32(KVCM_ATTN_PREPARE_ARGS) {
   return launch_attn_prepare<float>(make_params(proj, ldp, bias, wq, wk, positions, inv_freq, rot, head_norm, eps, v_keep,
                                                 v_first, lambda, slot_mapping, block_size, q_out, k_cache, v_cache, rows, nh,
-                                                nkv, dk, dv, HD, stream), rows, (cudaStream_t)stream);
+                                                nkv, dk, dv, HD, interleaved, v_inv_freq, stream), rows, (cudaStream_t)stream);
 }
 KVCM_API int kvcm_attn_prepare_bf16(KVCM_ATTN_PREPARE_ARGS) {
   return launch_attn_prepare<bf16>(make_params(proj, ldp, bias, wq, wk, positions, inv_freq, rot, head_norm, eps, v_keep,
                                                v_first, lambda, slot_mapping, block_size, q_out, k_cache, v_cache, rows, nh,
-                                               nkv, dk, dv, HD, stream), rows, (cudaStream_t)stream);
+                                               nkv, dk, dv, HD, interleaved, v_inv_freq, stream), rows, (cudaStream_t)stream);
 }

@@ -220,6 +220,8 @@ __device__ __forceinline__ void dr_copy16(float* dst, const float* src, bool ok)
 //   kScanDeltaChannel the same with channel-wise decays: row i of a head's S is scaled by gd[i]
 //   kScanLinear       S <- g S + k (beta v)^T;  o = S^T q        (no correction by the state's own
 //                     read-out: the selective state-space recurrence with k = B, q = C, beta = dt, v = x)
+//   kScanLinearChannel  S <- diag(gd) S + k (beta v)^T;  o = S^T q   (the linear form with channel-wise decays:
+//                     gated linear attention; `beta` may be null and then counts as one)
 // Where q, k and v of a row lie is given by `q_base`, `k_base`, `v_base` (floats from the row's start).
 struct ScanArgs {
   const float* qkv; int channels; int q_base, k_base, v_base;
@@ -230,7 +232,7 @@ struct ScanArgs {
   const int* seq_q_start; const int* seq_q_len; const int* seq_state_slot;
   float* out; int heads, qk_heads, dk, dv;
 };
-constexpr int kScanDelta = 0, kScanDeltaChannel = 1, kScanLinear = 2;
+constexpr int kScanDelta = 0, kScanDeltaChannel = 1, kScanLinear = 2, kScanLinearChannel = 3;
 
 template <int DR_COLS, int DR_LANES, int NI, int TT, bool EARLY, int MODE>
 __global__ void __launch_bounds__(DR_COLS * DR_LANES)
@@ -243,7 +245,8 @@ delta_scan_kernel(const ScanArgs A) {
   const int* __restrict__ seq_q_len = A.seq_q_len;
   const int* __restrict__ seq_state_slot = A.seq_state_slot;
   float* __restrict__ out = A.out;
-  constexpr bool CHD = MODE == kScanDeltaChannel;
+  constexpr bool CHD = MODE == kScanDeltaChannel || MODE == kScanLinearChannel;
+  constexpr bool LIN = MODE == kScanLinear || MODE == kScanLinearChannel;
   constexpr int DKP = DR_LANES * NI;
   constexpr int CPW = 32 / DR_LANES;                      // columns per warp
   // A token's q and k lie in shared memory as in global memory, in 16-byte pieces (so that they are
@@ -321,7 +324,8 @@ delta_scan_kernel(const ScanArgs A) {
     }
     for (int t = threadIdx.x; t < TT; t += blockDim.x) {
       const bool ok = t < nt;
-      dr_copy4(&bs[buf][t], A.beta + (ok ? size_t(q0 + t0 + t) * A.beta_ld + head : 0), ok);
+      if (A.beta) dr_copy4(&bs[buf][t], A.beta + (ok ? size_t(q0 + t0 + t) * A.beta_ld + head : 0), ok);
+      else bs[buf][t] = 1.f;
       if constexpr (!CHD) dr_copy4(&gs[buf][t], A.g + (ok ? size_t(q0 + t0 + t) * A.g_ld + head : 0), ok);
     }
     if constexpr (CHD) {
@@ -349,7 +353,7 @@ delta_scan_kernel(const ScanArgs A) {
     asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     __syncthreads();                                   // this tile has landed; the other buffer has been consumed
     if (t0 + TT < n) stage(buf ^ 1, t0 + TT);
-#pragma unroll(MODE == kScanLinear ? 4 : 1)
+#pragma unroll(LIN ? 4 : 1)
     for (int t = 0; t < nt; ++t) {
       const float g = CHD ? 1.f : gs[buf][t], beta = bs[buf][t];
       float kt[NI], qt[NI];
@@ -403,7 +407,7 @@ delta_scan_kernel(const ScanArgs A) {
       } else {
         // In the order of the definition; four partial sums each keep the chains of dependent FMAs short.
         float u;
-        if constexpr (MODE == kScanLinear) {
+        if constexpr (LIN) {
           u = beta * vs[buf][t][col_local];
         } else {
           float p4[4] = {0.f, 0.f, 0.f, 0.f};
@@ -529,14 +533,16 @@ static int launch_scan(const ScanArgs& A, int rows, int seqs, cudaStream_t s) {
   const int cols = per32 >= sms ? 32 : (2 * per32 >= sms ? 16 : 8);
   // few warps for the device (one request's long portion with few heads): the form with the shorter chain
   // (it has no meaning for the linear recurrence, whose step does not read the state)
-  const bool early = MODE != kScanLinear && per32 * 8 <= 4LL * sms;
+  constexpr bool LIN = MODE == kScanLinear || MODE == kScanLinearChannel;
+  constexpr bool CHD = MODE == kScanDeltaChannel || MODE == kScanLinearChannel;
+  const bool early = !LIN && per32 * 8 <= 4LL * sms;
   // with a decay per channel a third staged array shares the static shared memory: fewer tokens a tile
-  constexpr int TT_LONG = MODE == kScanDeltaChannel ? 8 : 16, TT_LONGEST = MODE == kScanDeltaChannel ? 4 : 8;
+  constexpr int TT_LONG = CHD ? 8 : 16, TT_LONGEST = CHD ? 4 : 8;
 #define KVCM_SCAN_E(COLS, LANES, NI, TT, EARLY)                                                                     \
   delta_scan_kernel<COLS, LANES, NI, TT, EARLY, MODE><<<dim3((dv + COLS - 1) / COLS, heads, seqs), COLS * LANES, 0, s>>>(A)
 #define KVCM_SCAN_C(COLS, LANES, NI, TT)                                                                            \
   do {                                                                                                              \
-    if constexpr (MODE == kScanLinear) KVCM_SCAN_E(COLS, LANES, NI, TT, false);                                     \
+    if constexpr (LIN) KVCM_SCAN_E(COLS, LANES, NI, TT, false);                                                     \
     else if (early) KVCM_SCAN_E(COLS, LANES, NI, TT, true);                                                         \
     else KVCM_SCAN_E(COLS, LANES, NI, TT, false);                                                                   \
   } while (0)
@@ -564,7 +570,7 @@ static int launch_scan(const ScanArgs& A, int rows, int seqs, cudaStream_t s) {
 }
 
 // mode: 0 delta rule with one decay per head (g), 1 delta rule with a decay per head and key channel (gd),
-// 2 linear recurrence (see the kernel).  The row layout of `qkv` is given by the three bases.
+// 2 linear recurrence, 3 linear recurrence with a decay per head and key channel (see the kernel).  The row layout of `qkv` is given by the three bases.
 KVCM_API int kvcm_state_scan(int mode, const float* qkv, int channels, int q_base, int k_base, int v_base,
                              const float* beta, int beta_ld, const float* g, int g_ld, const float* gd, float* state,
                              long long state_stride, const int* seq_q_start, const int* seq_q_len,
@@ -572,7 +578,8 @@ KVCM_API int kvcm_state_scan(int mode, const float* qkv, int channels, int q_bas
                              int dv, void* stream) {
   if (seqs == 0) return 0;
   if (dk < 1 || dk > 256 || qk_heads < 1 || heads % qk_heads) return KVCM_ERR_UNSUPPORTED;
-  if ((mode == kScanDeltaChannel) != (gd != nullptr) || (mode != kScanDeltaChannel && !g) || !beta) return KVCM_ERR_UNSUPPORTED;
+  const bool channel = mode == kScanDeltaChannel || mode == kScanLinearChannel;
+  if (channel != (gd != nullptr) || (!channel && !g) || (!beta && mode != kScanLinearChannel)) return KVCM_ERR_UNSUPPORTED;
   ScanArgs A;
   A.qkv = qkv; A.channels = channels; A.q_base = q_base; A.k_base = k_base; A.v_base = v_base;
   A.beta = beta; A.beta_ld = beta_ld; A.g = g; A.g_ld = g_ld; A.gd = gd; A.state = state; A.state_stride = state_stride;
@@ -582,6 +589,7 @@ KVCM_API int kvcm_state_scan(int mode, const float* qkv, int channels, int q_bas
   if (mode == kScanDelta) return launch_scan<kScanDelta>(A, rows, seqs, s);
   if (mode == kScanDeltaChannel) return launch_scan<kScanDeltaChannel>(A, rows, seqs, s);
   if (mode == kScanLinear) return launch_scan<kScanLinear>(A, rows, seqs, s);
+  if (mode == kScanLinearChannel) return launch_scan<kScanLinearChannel>(A, rows, seqs, s);
   return KVCM_ERR_UNSUPPORTED;
 }
 

@@ -141,6 +141,9 @@ class ModelRunner:
         x = spec.embedding.forward(ctx)
         pending = None
         for k, call in enumerate(spec.order):
+            if call.enter is not None:
+                part, arg = call.enter
+                x, pending = part.forward(x, pending, ctx, arg)
             pending = spec.blocks[call.layer].forward(x, pending, ctx, self.pools.sites[k])
         n = ctx.logit_rows.numel()
         if n == 0:

@@ -287,11 +287,11 @@ def gemm_plain(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor) -> None:
 def attention_plain(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                     block_tables: torch.Tensor, row_seq: torch.Tensor, positions: torch.Tensor,
                     nh: int, nkv: int, hd: int, scale: float, window: int = 0, softcap: float = 0.0,
-                    sink: Optional[torch.Tensor] = None) -> None:
+                    sink: Optional[torch.Tensor] = None, keep_first: int = 0) -> None:
     """Row-per-query paged attention.  q: [T, >= nh*hd] (row stride free), out: [T, nh*hd];
     caches [pages, nkv, block, hd]; block_tables int32 [S, max_blocks].  ``softcap`` > 0 caps the
     scaled scores as cap * tanh(score / cap); ``sink`` (float32 [nh]) adds exp(sink) of each head to
-    its softmax denominators."""
+    its softmax denominators; with a window, ``keep_first`` > 0 keeps a request's first keys visible to every row."""
     _cuda(q, out, k_cache, v_cache, block_tables, row_seq, positions, sink)
     _need(sink is None or (sink.dtype == torch.float32 and sink.is_contiguous() and sink.numel() == nh),
           "attention: sink float32 [heads]")
@@ -304,10 +304,10 @@ def attention_plain(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
           "attention: block_tables int32 [S, max_blocks]")
     _need(row_seq.dtype == _I32 and positions.dtype == _I32 and row_seq.numel() >= T
           and positions.numel() >= T, "attention: row_seq/positions int32 [T]")
-    fn = getattr(_lib(), "kvcm_attention_plain_" + _suffix(q))
+    fn = getattr(_lib(), "kvcm_attention_plain_keep_" + _suffix(q))
     _check(fn(_p(q), q.stride(0), _p(out), out.stride(0), _p(k_cache), _p(v_cache), _p(block_tables),
               block_tables.shape[1], _p(row_seq), _p(positions), T, nh, nkv, hd, k_cache.shape[2],
-              ctypes.c_float(scale), int(window), ctypes.c_float(softcap), _p(sink), _stream()), "attention_plain",
+              ctypes.c_float(scale), int(window), ctypes.c_float(softcap), _p(sink), int(keep_first), _stream()), "attention_plain",
            f"(hd={hd}, nh={nh}, nkv={nkv})")
 
 
@@ -390,20 +390,23 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, seed: torch.Tensor,
 
 def paged_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                     block_tables: torch.Tensor, ctx, nh: int, nkv: int, hd: int, scale: float,
-                    window: int = 0, softcap: float = 0.0, sink: Optional[torch.Tensor] = None) -> None:
+                    window: int = 0, softcap: float = 0.0, sink: Optional[torch.Tensor] = None,
+                    keep_first: int = 0) -> None:
     """Attention of all rows of a step.  Rows [0, ctx.decode_seqs) are single-row entries, the
     rest are the rows of longer portions.  ``ctx.options['attention']``: 'plain' forces the plain
     kernel for every row; float32 storage always uses it (the true 32-bit path)."""
     mode = ctx.options.get("attention", "auto")
     if mode == "plain" or q.dtype == torch.float32 or not fast_attention_supported(nh, nkv, hd, k_cache.shape[2]):
         attention_plain(q, out, k_cache, v_cache, block_tables, ctx.row_seq, ctx.positions,
-                        nh, nkv, hd, scale, window, softcap, sink)
+                        nh, nkv, hd, scale, window, softcap, sink, keep_first)
         return
     nd = ctx.decode_seqs
     if nd > 0:
-        attention_decode(q[:nd], out[:nd], k_cache, v_cache, block_tables, ctx, nh, nkv, hd, scale, window, softcap, sink)
+        attention_decode(q[:nd], out[:nd], k_cache, v_cache, block_tables, ctx, nh, nkv, hd, scale, window, softcap, sink,
+                         keep_first)
     if ctx.rows > nd:
-        attention_prefill(q, out, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, scale, window, softcap, sink)
+        attention_prefill(q, out, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, scale, window, softcap, sink,
+                          keep_first)
 
 
 def fast_attention_supported(nh: int, nkv: int, hd: int, block_size: int) -> bool:
@@ -465,7 +468,8 @@ def decode_partitions(seqs: int, nh: int, nkv: int, hd: int, max_ctx: int, devic
 
 def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                      block_tables: torch.Tensor, ctx, nh: int, nkv: int, hd: int, scale: float,
-                     window: int = 0, softcap: float = 0.0, sink: Optional[torch.Tensor] = None) -> None:
+                     window: int = 0, softcap: float = 0.0, sink: Optional[torch.Tensor] = None,
+                     keep_first: int = 0) -> None:
     """Single-row entries: q/out hold one row per request, in the order of the batch's entries.
     ``softcap`` / ``sink`` as in ``attention_plain``."""
     _cuda(q, out, k_cache, v_cache, block_tables, sink)
@@ -486,10 +490,10 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, 
     if parts > 1 and not in_cluster:
         n = S * nh * parts * (hd + 2)          # partial outputs + (max, sum) per partition
         scratch = torch.empty(n, dtype=torch.float32, device=q.device)
-    rc = _lib().kvcm_attention_decode_capped_bf16(
+    rc = _lib().kvcm_attention_decode_keep_bf16(
         _p(q), q.stride(0), _p(out), out.stride(0), _p(k_cache), _p(v_cache), _p(block_tables),
         block_tables.shape[1], _p(ctx.seq_ctx_len), S, nh, nkv, hd, k_cache.shape[2],
-        ctypes.c_float(scale), int(window), size, parts, _p(scratch), int(in_cluster), ctypes.c_float(softcap), _p(sink),
+        ctypes.c_float(scale), int(window), int(keep_first), size, parts, _p(scratch), int(in_cluster), ctypes.c_float(softcap), _p(sink),
         _stream())
     _check(rc, "attention_decode", f"(hd={hd}, nh={nh}, nkv={nkv})")
     if parts > 1 and not in_cluster:
@@ -499,7 +503,8 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, 
 
 def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                       block_tables: torch.Tensor, ctx, nh: int, nkv: int, hd: int, scale: float,
-                      window: int = 0, softcap: float = 0.0, sink: Optional[torch.Tensor] = None) -> None:
+                      window: int = 0, softcap: float = 0.0, sink: Optional[torch.Tensor] = None,
+                      keep_first: int = 0) -> None:
     """Rows of portions longer than one token; q/out are the step's full row arrays.
     ``ctx.options['attn_prefill']``: 'tcgen05' | 'mma' force a kernel; 'auto' takes the tcgen05
     kernel where it supports the sizes (head_dim 64 or 128; pages of 8 to 64 keys dividing 64, or multiples of 64)."""
@@ -514,7 +519,8 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
     _need(ctx.tile_rows == 64, "attention_prefill: the batch must be tiled in 64 query rows")
     mode = ctx.options.get("attn_prefill", "auto")
     B = k_cache.shape[2]
-    if mode != "mma" and (mode == "tcgen05" or prefill_tcgen05_supported(hd, B)):
+    kept = int(keep_first) if window > 0 else 0          # the tcgen05 kernel walks one run of keys per row tile
+    if kept == 0 and mode != "mma" and (mode == "tcgen05" or prefill_tcgen05_supported(hd, B)):
         _need(out.data_ptr() % 16 == 0 and out.stride(0) % 8 == 0, "attention_prefill: out rows must be 16-byte aligned")
         rc = _lib().kvcm_attention_prefill_tcgen05_bf16(
             _p(q), q.stride(0), q.shape[0], _p(out), out.stride(0), _p(k_cache), _p(v_cache), k_cache.shape[0],
@@ -523,11 +529,11 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
             int(window), ctypes.c_float(softcap), _p(sink), _stream())
         _check(rc, "attention_prefill_tcgen05", f"(hd={hd}, nh={nh}, nkv={nkv}, block={B})")
         return
-    rc = _lib().kvcm_attention_prefill_bf16(
+    rc = _lib().kvcm_attention_prefill_keep_bf16(
         _p(q), q.stride(0), _p(out), out.stride(0), _p(k_cache), _p(v_cache), _p(block_tables),
         block_tables.shape[1], _p(ctx.tile_seq), _p(ctx.tile_q0), _p(ctx.seq_q_start), _p(ctx.seq_q_len),
         _p(ctx.seq_ctx_len), ctx.prefill_tiles, nh, nkv, hd, B, ctypes.c_float(scale),
-        int(window), ctypes.c_float(softcap), _p(sink), _stream())
+        int(window), kept, ctypes.c_float(softcap), _p(sink), _stream())
     _check(rc, "attention_prefill", f"(hd={hd}, nh={nh}, nkv={nkv})")
 
 
@@ -1114,26 +1120,27 @@ def moe_combine(y: torch.Tensor, work: torch.Tensor, wt: torch.Tensor, experts: 
 
 # ------------------------------------------------- recurrences beside the head-wise delta rule
 
-SCAN_DELTA, SCAN_DELTA_CHANNEL, SCAN_LINEAR = 0, 1, 2
+SCAN_DELTA, SCAN_DELTA_CHANNEL, SCAN_LINEAR, SCAN_LINEAR_CHANNEL = 0, 1, 2, 3
 
 
-def state_scan(mode: int, qkv: torch.Tensor, bases, beta: torch.Tensor, g: Optional[torch.Tensor],
+def state_scan(mode: int, qkv: torch.Tensor, bases, beta: Optional[torch.Tensor], g: Optional[torch.Tensor],
                gd: Optional[torch.Tensor], state: torch.Tensor, ctx, out: torch.Tensor, heads: int, qk_heads: int,
                dk: int, dv: int) -> None:
     """The matrix-state recurrences over every request's rows of the step, from and into its state row
     (csrc/cuda/delta_rule.cu).  ``bases`` = where a row's q, k and v start; ``beta`` [T, >= heads] (a view
     with a row stride is fine), ``g`` likewise (one decay per head) or ``gd`` [T, heads*dk] (one per head
-    and key channel)."""
+    and key channel).  ``beta`` may be None for SCAN_LINEAR_CHANNEL (it then counts as one)."""
     _cuda(qkv, beta, g, gd, state, out)
     _need(all(t is None or t.dtype == torch.float32 for t in (qkv, beta, g, gd, state, out)), "state_scan: float32")
-    _need(qkv.is_contiguous() and out.is_contiguous() and state.is_contiguous() and beta.stride(1) == 1
+    _need(beta is not None or mode == SCAN_LINEAR_CHANNEL, "state_scan: beta")
+    _need(qkv.is_contiguous() and out.is_contiguous() and state.is_contiguous() and (beta is None or beta.stride(1) == 1)
           and (g is None or g.stride(1) == 1) and (gd is None or (gd.is_contiguous() and gd.shape == (qkv.shape[0], heads * dk))),
           "state_scan: layout")
     qb, kb, vb = (int(b) for b in bases)
     C = qkv.shape[1]
     _need(max(qb, kb) + qk_heads * dk <= C and vb + heads * dv <= C and out.shape == (qkv.shape[0], heads * dv)
-          and state.shape[1] >= heads * dk * dv and beta.shape[1] >= heads, "state_scan: shapes")
-    _check(_lib().kvcm_state_scan(int(mode), _p(qkv), C, qb, kb, vb, _p(beta), beta.stride(0), _p(g),
+          and state.shape[1] >= heads * dk * dv and (beta is None or beta.shape[1] >= heads), "state_scan: shapes")
+    _check(_lib().kvcm_state_scan(int(mode), _p(qkv), C, qb, kb, vb, _p(beta), beta.stride(0) if beta is not None else 0, _p(g),
                                   g.stride(0) if g is not None else 0, _p(gd), _p(state), _ll(state.stride(0)),
                                   _p(ctx.seq_q_start), _p(ctx.seq_q_len), _p(ctx.seq_state_slot), _p(out), qkv.shape[0],
                                   ctx.seqs, heads, qk_heads, dk, dv, _stream()), "state_scan", f"(mode={mode}, dk={dk}, dv={dv})")
@@ -1227,13 +1234,17 @@ def attn_prepare(proj: torch.Tensor, bias: Optional[torch.Tensor], wq: Optional[
                  positions: torch.Tensor, inv_freq: Optional[torch.Tensor], rot: int, head_norm: bool, eps: float,
                  v_keep: Optional[torch.Tensor], v_first: Optional[torch.Tensor], lam: Optional[torch.Tensor],
                  slot_mapping: Optional[torch.Tensor], q_out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
-                 nh: int, nkv: int, dk: int, dv: int) -> None:
+                 nh: int, nkv: int, dk: int, dv: int, interleaved: bool = False,
+                 v_inv_freq: Optional[torch.Tensor] = None) -> None:
     """From the float32 q|k|v projection of a step's rows to the attention kernel's inputs: optional bias,
     optional norm over the whole q and k projections (weights wq, wk), rotation of the first ``rot``
     dimensions of every head, optional per-head norm without weights, optional mixing of the values with
     ``v_first`` by ``lam``; q to ``q_out`` [T, nh*HD] and k, v to the rows' page slots, padded with zeros to the
-    cache's head size HD (csrc/cuda/attn_prepare.cu)."""
-    _cuda(proj, bias, wq, wk, positions, inv_freq, v_keep, v_first, lam, slot_mapping, q_out, k_cache, v_cache)
+    cache's head size HD (csrc/cuda/attn_prepare.cu).  ``interleaved``: rotary pairs (2i, 2i+1) instead of
+    (i, i + rot/2); ``v_inv_freq`` (float32 [dv/2]): the values too are turned by their position, over all dv."""
+    _cuda(proj, bias, wq, wk, positions, inv_freq, v_keep, v_first, lam, slot_mapping, q_out, k_cache, v_cache, v_inv_freq)
+    _need(v_inv_freq is None or (v_inv_freq.dtype == torch.float32 and v_inv_freq.is_contiguous() and v_inv_freq.numel() * 2 == dv),
+          "attn_prepare: v_inv_freq float32 [dv/2]")
     T = q_out.shape[0]
     HD, B = k_cache.shape[3], k_cache.shape[2]
     n = nh * dk + nkv * dk + nkv * dv
@@ -1252,4 +1263,149 @@ def attn_prepare(proj: torch.Tensor, bias: Optional[torch.Tensor], wq: Optional[
     fn = getattr(_lib(), "kvcm_attn_prepare_" + _suffix(q_out))
     _check(fn(_p(proj), proj.stride(0), _p(bias), _p(wq), _p(wk), _p(positions), _p(inv_freq), int(rot), int(bool(head_norm)),
               ctypes.c_float(eps), _p(v_keep), _p(v_first), _p(lam), _p(slot_mapping), B, _p(q_out), _p(k_cache), _p(v_cache),
-              T, nh, nkv, dk, dv, HD, _stream()), "attn_prepare", f"(nh={nh}, nkv={nkv}, dk={dk}, dv={dv}, HD={HD})")
+              T, nh, nkv, dk, dv, HD, int(bool(interleaved)), _p(v_inv_freq), _stream()), "attn_prepare", f"(nh={nh}, nkv={nkv}, dk={dk}, dv={dv}, HD={HD})")
+
+
+# ------------------------------------------- blocks normalised on both sides, and what comes with them
+
+def embed_scaled(ids: torch.Tensor, table: torch.Tensor, x: torch.Tensor, keep: Optional[torch.Tensor], scale: float) -> None:
+    """x[t, :] = float(table[ids[t], :]) * scale; ``keep`` (optional, float32 like x) receives the same rows."""
+    _cuda(ids, table, x, keep)
+    T, H = x.shape
+    _need(ids.dtype == _I32 and ids.numel() >= T and x.dtype == torch.float32 and x.is_contiguous() and table.is_contiguous()
+          and table.shape[1] == H and (keep is None or (keep.dtype == torch.float32 and keep.is_contiguous() and keep.shape == x.shape)),
+          "embed_scaled: layout")
+    fn = getattr(_lib(), "kvcm_embed_scaled_" + _suffix(table))
+    _check(fn(_p(ids), _p(table), _p(x), _p(keep), T, H, table.shape[0], ctypes.c_float(scale), _stream()), "embed_scaled")
+
+
+def norm_post_pre(x: torch.Tensor, y: Optional[torch.Tensor], post_w: Optional[torch.Tensor], pre_w: Optional[torch.Tensor],
+                  out: Optional[torch.Tensor], eps: float, rows: Optional[torch.Tensor] = None) -> None:
+    """The norm that closes a sublayer and the norm that opens the next one, in one pass over a row:
+    x += post_w * y / rms(y) (when ``y`` is given; float32 like x), then out = pre_w * x / rms(x) (when ``out`` is
+    given; storage dtype).  Weights are the multipliers themselves, float32 [H].  ``rows`` gathers: the norms are
+    formed for rows[i] only, ``out`` has one row per index and x is left as it is."""
+    _cuda(x, y, post_w, pre_w, out, rows)
+    T, H = x.shape
+    _need(x.dtype == torch.float32 and x.is_contiguous(), "norm_post_pre: x float32 [T, H]")
+    _need(y is None or (y.dtype == torch.float32 and y.is_contiguous() and y.shape == x.shape and post_w is not None),
+          "norm_post_pre: y float32 like x, with its weight")
+    for w in (post_w, pre_w):
+        _need(w is None or (w.dtype == torch.float32 and w.is_contiguous() and w.numel() == H), "norm_post_pre: weights float32 [H]")
+    _need(out is not None or y is not None, "norm_post_pre: nothing to do")
+    _need(out is None or (out.is_contiguous() and out.shape[1] == H and pre_w is not None), "norm_post_pre: out")
+    n = T
+    if rows is not None:
+        _need(out is not None and rows.dtype == _I32 and rows.numel() >= out.shape[0], "norm_post_pre: rows int32 [n]")
+        n = out.shape[0]
+    elif out is not None:
+        _need(out.shape[0] == T, "norm_post_pre: out rows != x rows")
+    store = out.dtype if out is not None else torch.float32
+    fn = getattr(_lib(), "kvcm_norm_post_pre_" + _SUFFIX[store])
+    _check(fn(_p(x), _p(y), _p(post_w), _p(pre_w), _p(out), _p(rows), n, H, ctypes.c_float(eps), _stream()), "norm_post_pre",
+           f"(hidden={H})")
+
+
+def poly_norm_act(z: torch.Tensor, coef: torch.Tensor, out: torch.Tensor, eps: float) -> None:
+    """out = a N(z) + b N(z^2) + c N(z^3) + e row by row, N(v) = v / sqrt(mean(v^2) + eps), powers element-wise;
+    z float32 [T, F] (rows may be strided), coef float32 [4] = (a, b, c, e), out [T, F] in the storage dtype."""
+    _cuda(z, coef, out)
+    T, F = out.shape
+    _need(z.dtype == torch.float32 and z.stride(1) == 1 and z.shape == out.shape and out.is_contiguous()
+          and coef.dtype == torch.float32 and coef.is_contiguous() and coef.numel() == 4, "poly_norm_act: layout")
+    fn = getattr(_lib(), "kvcm_poly_norm_act_" + _suffix(out))
+    _check(fn(_p(z), z.stride(0), _p(coef), _p(out), T, F, ctypes.c_float(eps), _stream()), "poly_norm_act", f"(ff={F})")
+
+
+def concat_cast(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t] = [a[t] | b[t]] in out's dtype; a, b float32 [T, H], out [T, 2H]."""
+    _cuda(a, b, out)
+    T, H = a.shape
+    _need(a.dtype == b.dtype == torch.float32 and a.is_contiguous() and b.is_contiguous() and b.shape == a.shape
+          and out.is_contiguous() and out.shape == (T, 2 * H), "concat_cast: layout")
+    fn = getattr(_lib(), "kvcm_concat_cast_" + _suffix(out))
+    _check(fn(_p(a), _p(b), _p(out), T, H, _stream()), "concat_cast")
+
+
+def add_bias_rows(x: torch.Tensor, bias: torch.Tensor) -> None:
+    """x[t, :] += bias, float32."""
+    _cuda(x, bias)
+    _need(x.dtype == bias.dtype == torch.float32 and x.is_contiguous() and bias.is_contiguous() and bias.numel() == x.shape[1],
+          "add_bias_rows: layout")
+    _check(_lib().kvcm_add_bias_rows(_p(x), _p(bias), x.shape[0], x.shape[1], _stream()), "add_bias_rows")
+
+
+def softcap_rows(x: torch.Tensor, cap: float) -> None:
+    """x <- cap * tanh(x / cap) in place, float32."""
+    _cuda(x)
+    _need(x.dtype == torch.float32 and x.is_contiguous(), "softcap_rows: float32")
+    _check(_lib().kvcm_softcap_rows(_p(x), _ll(x.numel()), ctypes.c_float(cap), _stream()), "softcap_rows")
+
+
+def rotate_heads(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor, heads: int, head_dim: int,
+                 interleaved: bool, sign: float = 1.0) -> None:
+    """In place: the first 2 * len(inv_freq) elements of every head of row t turn by sign * positions[t] * inv_freq[i],
+    pairs (2i, 2i+1) when ``interleaved`` else (i, i + n/2).  x [T, >= heads*head_dim] in either storage dtype;
+    angles and the turn in float32."""
+    _cuda(x, positions, inv_freq)
+    T = x.shape[0]
+    n = 2 * inv_freq.numel()
+    _need(x.stride(1) == 1 and x.shape[1] >= heads * head_dim and inv_freq.dtype == torch.float32 and inv_freq.is_contiguous()
+          and n <= head_dim and positions.dtype == _I32 and positions.numel() >= T, "rotate_heads: layout")
+    fn = getattr(_lib(), "kvcm_rotate_heads_" + _suffix(x))
+    _check(fn(_p(x), x.stride(0), _p(positions), _p(inv_freq), n, int(bool(interleaved)), ctypes.c_float(sign), T, heads,
+              head_dim, _stream()), "rotate_heads")
+
+
+def gla_prepare(qkv: torch.Tensor, q_base: int, n_q: int, qscale: float, z: torch.Tensor, bias: Optional[torch.Tensor],
+                tau: float) -> None:
+    """In place, float32: the n_q query elements of every row of ``qkv`` from ``q_base`` on are scaled by ``qscale``;
+    ``z`` [T, heads*dk] becomes the decays sigmoid(z + bias)^(1/tau)."""
+    _cuda(qkv, z, bias)
+    T = qkv.shape[0]
+    _need(qkv.dtype == z.dtype == torch.float32 and qkv.is_contiguous() and z.is_contiguous() and z.shape[0] == T
+          and q_base + n_q <= qkv.shape[1] and (bias is None or (bias.dtype == torch.float32 and bias.is_contiguous()
+                                                              and bias.numel() == z.shape[1])), "gla_prepare: layout")
+    _check(_lib().kvcm_gla_prepare(_p(qkv), qkv.shape[1], int(q_base), int(n_q), ctypes.c_float(qscale), _p(z), _p(bias),
+                                   z.shape[1], ctypes.c_float(tau), T, _stream()), "gla_prepare")
+
+
+def latent_rope_cache(proj: torch.Tensor, wq: Optional[torch.Tensor], wc: torch.Tensor, positions: torch.Tensor,
+                      inv_freq: torch.Tensor, interleaved: bool, slot_mapping: torch.Tensor, cq_out: Optional[torch.Tensor],
+                      cache: torch.Tensor, q_rank: int, rank: int, rot_dim: int, eps: float) -> None:
+    """Rows of ``proj`` (float32) are [dq: q_rank | c: rank | kr: rot_dim].  cq_out = wq * dq / rms(dq) (storage
+    dtype; q_rank == 0: none); the row's page slot of ``cache`` [pages, 1, page, HD] becomes
+    [wc * c / rms(c) | kr with its first 2 * len(inv_freq) elements turned by the position | zeros]."""
+    _cuda(proj, wq, wc, positions, inv_freq, slot_mapping, cq_out, cache)
+    T = proj.shape[0]
+    HD = cache.shape[3]
+    _need(proj.dtype == torch.float32 and proj.stride(1) == 1 and proj.shape[1] >= q_rank + rank + rot_dim, "latent_rope_cache: proj")
+    _need(cache.is_contiguous() and cache.shape[1] == 1 and HD >= rank + rot_dim, "latent_rope_cache: cache pages [pages, 1, page, HD]")
+    _need(wc.dtype == torch.float32 and wc.numel() == rank and inv_freq.dtype == torch.float32 and 2 * inv_freq.numel() <= rot_dim,
+          "latent_rope_cache: weights")
+    if q_rank:
+        _need(wq is not None and wq.dtype == torch.float32 and wq.numel() == q_rank and cq_out is not None and cq_out.is_contiguous()
+              and cq_out.shape == (T, q_rank) and cq_out.dtype == cache.dtype, "latent_rope_cache: the query's latent")
+    _need(positions.dtype == _I32 and slot_mapping.dtype == _I32 and positions.numel() >= T and slot_mapping.numel() >= T,
+          "latent_rope_cache: positions / slot_mapping int32 [T]")
+    fn = getattr(_lib(), "kvcm_latent_rope_cache_" + _suffix(cache))
+    _check(fn(_p(proj), proj.stride(0), _p(wq), _p(wc), _p(positions), _p(inv_freq), 2 * inv_freq.numel(), int(bool(interleaved)),
+              _p(slot_mapping), _p(cq_out), _p(cache), T, int(q_rank), int(rank), int(rot_dim), HD, ctypes.c_float(eps), _stream()),
+           "latent_rope_cache")
+
+
+def latent_q_rope(q: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor, interleaved: bool, qn_out: torch.Tensor,
+                  qrow: torch.Tensor, heads: int, dn: int, dr: int, rank: int) -> None:
+    """Rows of ``q`` (float32) hold per head [unrotated: dn | rotated: dr].  qn_out [T, heads, dn] receives the
+    unrotated parts in the storage dtype; qrow [T, heads, HD] receives at [rank : rank + dr] the rotated part turned by
+    the position and zeros behind it ([0 : rank] is left for the map into the latent space)."""
+    _cuda(q, positions, inv_freq, qn_out, qrow)
+    T = q.shape[0]
+    HD = qrow.shape[2]
+    _need(q.dtype == torch.float32 and q.stride(1) == 1 and q.shape[1] >= heads * (dn + dr) and qn_out.is_contiguous()
+          and qn_out.shape == (T, heads, dn) and qrow.is_contiguous() and qrow.shape[:2] == (T, heads) and HD >= rank + dr
+          and qn_out.dtype == qrow.dtype and inv_freq.dtype == torch.float32 and 2 * inv_freq.numel() <= dr
+          and positions.dtype == _I32 and positions.numel() >= T, "latent_q_rope: layout")
+    fn = getattr(_lib(), "kvcm_latent_q_rope_" + _suffix(qrow))
+    _check(fn(_p(q), q.stride(0), _p(positions), _p(inv_freq), 2 * inv_freq.numel(), int(bool(interleaved)), _p(qn_out), _p(qrow),
+              T, heads, dn, dr, int(rank), HD, _stream()), "latent_q_rope")

@@ -33,6 +33,7 @@ class ModelSpec:
     lm_head: Part
     bindings: List[TensorBinding] = field(default_factory=list)
     ignorable: Sequence[str] = ()          # substrings of checkpoint names that may be skipped
+    extras: List[Tuple[str, Part]] = field(default_factory=list)   # parts outside the layers (what run-order entries call on entry)
 
     def parts(self):
         yield "embedding", self.embedding
@@ -40,3 +41,4 @@ class ModelSpec:
             yield f"blocks.{i}", b
         yield "final_norm", self.final_norm
         yield "lm_head", self.lm_head
+        yield from self.extras

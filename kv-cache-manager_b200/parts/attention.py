@@ -84,11 +84,17 @@ class GeneralAttention(Mixer):
     * ``bias``: q, k and v projections with a bias;
     * ``proj_norm``: q <- w_q * q / sqrt(mean(q^2) + eps) over the WHOLE q projection (all heads at
       once), k likewise, before the rotation;
-    * a rotary ``position`` that may cover only the first dimensions of a head;
+    * a rotary ``position`` that may cover only the first dimensions of a head, in rotate-half or in
+      interleaved pairs;
+    * ``rotate_values``: every value is turned by its own position over all ``dv`` dimensions (frequencies
+      base^(-2m/dv) with the position encoding's base, the same pairing) before it is cached, and a head's
+      output at position i (the weighted sum of the turned values) is turned back by -i;
     * ``head_norm``: q and k of every head scaled to unit root mean square (no weights), after the
       rotation;
     * ``softcap``: score <- cap * tanh(score / cap) after the scale;
-    * ``window``: row i sees keys j with 0 <= i - j < window;
+    * ``window``: row i sees keys j with 0 <= i - j < window; with ``keep_first`` > 0 also every j < keep_first
+      (j <= i), at its true position.  Such a mixer asks for pages that are never given back: the cache
+      manager's windows release pages from the front, where the kept keys lie;
     * ``sink``: a learned number per head whose exponential joins the softmax's denominator (no key, no
       value, not scaled, not capped);
     * ``value_mix``: "source" leaves this layer's values (as projected) in ``ctx.shared[mix_key]`` for later
@@ -100,17 +106,23 @@ class GeneralAttention(Mixer):
     def __init__(self, hidden: int, num_heads: int, num_kv_heads: int, dk: int, dv: int,
                  position: PositionEncoding, scale: Optional[float] = None, window: int = 0, softcap: float = 0.0,
                  sink: bool = False, bias: bool = False, proj_norm: bool = False, head_norm: bool = False,
-                 norm_eps: float = 1e-6, value_mix: Optional[str] = None, mix_key: str = "v_first") -> None:
+                 norm_eps: float = 1e-6, value_mix: Optional[str] = None, mix_key: str = "v_first",
+                 rotate_values: bool = False, keep_first: int = 0) -> None:
         super().__init__()
         if num_kv_heads < 1 or num_heads % num_kv_heads:
             raise ValueError(f"attention: {num_heads} query heads are not a multiple of {num_kv_heads} KV heads")
         if value_mix not in (None, "source", "mix"):
             raise ValueError(f"attention: unknown value_mix {value_mix!r}")
-        if getattr(position, "interleaved", False) or getattr(position, "rotary_dim", 0) > dk:
-            raise ValueError("attention_general: rotate-half pairs within the head's own size only")
+        if getattr(position, "rotary_dim", 0) > dk:
+            raise ValueError("attention_general: the rotation covers at most the head's own size")
+        if rotate_values and (dv % 2 or not hasattr(position, "theta")):
+            raise ValueError("attention_general: rotated values need an even value size and a rotary position encoding")
         self.hidden, self.nh, self.nkv, self.dk, self.dv = hidden, num_heads, num_kv_heads, dk, dv
         self.hd = padded_head_dim(max(dk, dv))
         self.window, self.softcap = int(window or 0), float(softcap or 0.0)
+        self.keep_first = int(keep_first or 0) if self.window > 0 else 0
+        self.rotate_values = bool(rotate_values)
+        self._v_inv_freq = None
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(dk)
         self.has_sink, self.has_bias, self.proj_norm, self.head_norm = bool(sink), bool(bias), bool(proj_norm), bool(head_norm)
         self.norm_eps, self.value_mix, self.mix_key = float(norm_eps), value_mix, mix_key
@@ -131,12 +143,16 @@ class GeneralAttention(Mixer):
         self._o_weight = None
 
     def cache_spec(self) -> CacheSpec:
-        return CacheSpec(self.nkv, self.hd, self.window)
+        return CacheSpec(self.nkv, self.hd, 0 if self.keep_first > 0 else self.window)
 
     def prepare(self, device, dtype) -> None:
         super().prepare(device, dtype)
         self._f32 = {n: self.param(n).to(device=device, dtype=torch.float32).reshape(-1).contiguous()
                      for n in self.param_specs()}
+        if self.rotate_values:
+            m = torch.arange(self.dv // 2, dtype=torch.float64)
+            self._v_inv_freq = (1.0 / torch.pow(torch.tensor(self.position.theta, dtype=torch.float64),
+                                                2.0 * m / self.dv)).to(torch.float32).to(device)
         w = self.o.param("weight")
         if self.hd != self.dv:                              # zero columns where the attention output is padding
             wide = torch.zeros((self.hidden, self.nh, self.hd), dtype=w.dtype, device=w.device)
@@ -158,8 +174,10 @@ class GeneralAttention(Mixer):
         K.attn_prepare(proj, f.get("bias"), f.get("q_norm"), f.get("k_norm"), ctx.positions, pos.inv_freq,
                        pos.rotary_dim if pos.inv_freq is not None else 0, self.head_norm, self.norm_eps, keep, first,
                        f["vmix"] if first is not None else None, g.slot_mapping if site.writes else None, q, site.k, site.v,
-                       self.nh, self.nkv, self.dk, self.dv)
+                       self.nh, self.nkv, self.dk, self.dv, bool(getattr(pos, "interleaved", False)), self._v_inv_freq)
         out = torch.empty((T, self.nh * self.hd), dtype=h.dtype, device=h.device)
         K.paged_attention(q, out, site.k, site.v, g.block_tables, ctx, self.nh, self.nkv, self.hd, self.scale,
-                          self.window, self.softcap, f.get("sink"))
+                          self.window, self.softcap, f.get("sink"), self.keep_first)
+        if self.rotate_values:
+            K.rotate_heads(out, ctx.positions, self._v_inv_freq, self.nh, self.hd, bool(getattr(pos, "interleaved", False)), -1.0)
         return matmul_nt(out, self._o_weight, torch.float32, ctx.options)

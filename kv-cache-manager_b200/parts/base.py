@@ -123,9 +123,13 @@ class LayerCall:
     """One entry of the model's run order: which layer runs, and whose cache it uses.
 
     ``cache_of``: None = this call site has a cache of its own (and writes it); an integer =
-    the index (in the run order) of an earlier call site whose cache it reads without writing."""
+    the index (in the run order) of an earlier call site whose cache it reads without writing.
+    ``enter``: a part that works on the residual stream before the layer runs (``StreamPart``) with
+    the argument it is called with, e.g. the entry of a span of layers that runs several times and the
+    number of the pass."""
     layer: int
     cache_of: Optional[int] = None
+    enter: Optional[Tuple[Any, Any]] = None
 
 
 # -------------------------------------------------------------------------------- contexts
@@ -242,6 +246,14 @@ class Norm(Part):
 
 class PositionEncoding(Part):
     pass
+
+
+class StreamPart(Part):
+    """A part between two layers: ``forward(x, pending, ctx, arg) -> (x', pending')`` takes the float32
+    residual stream (and what the layer before left pending) and returns the stream the next layer reads."""
+
+    def forward(self, x: torch.Tensor, pending, ctx: StepContext, arg=None):
+        raise NotImplementedError
 
 
 class Block(Part):

@@ -87,3 +87,43 @@ class ParallelBlock(Block):
         if self.ffn is not None:
             out.append((self.ffn.forward(h, ctx, out_dtype=torch.float32), 1.0))
         return out
+
+
+@BLOCKS.register("sandwich")
+class SandwichBlock(Block):
+    """Every sublayer normalised on both sides: x += norm1b(mixer(norm1(x))); x += norm2b(ffn(norm2(x))).  The four
+    norms expose ``multiplier`` (float32 [hidden]) and ``eps`` ("rmsnorm_offset").  The sublayers return float32; the
+    norm that closes one sublayer and the norm that opens the next are one kernel (the closing norm of the
+    layer's last sublayer runs alone, so that the stream is complete when the layer ends; ``fuse`` off: every
+    norm is a launch of its own).  ``ffn`` may be None: a layer of a mixer only."""
+
+    def __init__(self, norm1: Norm, mixer: Mixer, norm1b: Norm, norm2: Optional[Norm] = None,
+                 ffn: Optional[FeedForward] = None, norm2b: Optional[Norm] = None) -> None:
+        super().__init__()
+        self.norm1 = self.add_child("norm1", norm1)
+        self.mixer = self.add_child("mixer", mixer)
+        self.norm1b = self.add_child("norm1b", norm1b)
+        self.norm2 = self.add_child("norm2", norm2) if norm2 is not None else None
+        self.ffn = self.add_child("ffn", ffn) if ffn is not None else None
+        self.norm2b = self.add_child("norm2b", norm2b) if norm2b is not None else None
+        if not ((self.norm2 is None) == (self.ffn is None) == (self.norm2b is None)):
+            raise ValueError("sandwich block: a feed-forward and its two norms come together")
+
+    def forward(self, x: torch.Tensor, pending: Optional[torch.Tensor], ctx: StepContext,
+                site: SiteCache) -> Optional[torch.Tensor]:
+        if pending is not None:
+            K.add_residual(x, pending)
+        h = torch.empty(x.shape, dtype=ctx.dtype, device=x.device)
+        K.norm_post_pre(x, None, None, self.norm1.multiplier, h, self.norm1.eps)
+        y = self.mixer.forward(h, ctx, site)
+        if self.ffn is None:
+            K.norm_post_pre(x, y, self.norm1b.multiplier, None, None, self.norm1b.eps)
+            return None
+        if ctx.options.get("fuse", True) and self.norm1b.eps == self.norm2.eps:
+            K.norm_post_pre(x, y, self.norm1b.multiplier, self.norm2.multiplier, h, self.norm2.eps)
+        else:
+            K.norm_post_pre(x, y, self.norm1b.multiplier, None, None, self.norm1b.eps)
+            K.norm_post_pre(x, None, None, self.norm2.multiplier, h, self.norm2.eps)
+        y = self.ffn.forward(h, ctx, out_dtype=torch.float32)
+        K.norm_post_pre(x, y, self.norm2b.multiplier, None, None, self.norm2b.eps)
+        return None

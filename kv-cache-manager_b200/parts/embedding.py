@@ -24,6 +24,24 @@ class Embedding(Part):
         return x
 
 
+class ScaledEmbedding(Part):
+    """x = table[token] * scale into the float32 residual stream.  With ``keep_as`` the same rows are also left
+    in ``ctx.shared[keep_as]`` (float32) for parts that read the embedding's output later in the step."""
+
+    def __init__(self, vocab: int, hidden: int, scale: float = 1.0, keep_as: Optional[str] = None) -> None:
+        super().__init__()
+        self.vocab, self.hidden, self.scale, self.keep_as = vocab, hidden, float(scale), keep_as
+        self.declare("weight", (vocab, hidden), ("normal", 0.02), "table")
+
+    def forward(self, ctx: StepContext) -> torch.Tensor:
+        x = torch.empty((ctx.rows, self.hidden), dtype=torch.float32, device=ctx.tokens.device)
+        keep = None
+        if self.keep_as:
+            keep = ctx.shared[self.keep_as] = torch.empty_like(x)
+        K.embed_scaled(ctx.tokens, self.param("weight"), x, keep, self.scale)
+        return x
+
+
 class SummedEmbedding(Part):
     """A sum of tables into the float32 residual stream: the token's row; optionally the row of a
     hashed table for the pair (previous token, token), row ``(prev * mul_prev + token * mul_cur) mod
@@ -54,12 +72,16 @@ class SummedEmbedding(Part):
 
 
 class LMHead(Part):
-    """logits = h W^T in float32.  ``weight`` may alias the embedding table (tied)."""
+    """logits = h W^T in float32.  ``weight`` may alias the embedding table (tied).  ``softcap`` > 0:
+    logits <- cap * tanh(logits / cap)."""
 
-    def __init__(self, hidden: int, vocab: int) -> None:
+    def __init__(self, hidden: int, vocab: int, softcap: float = 0.0) -> None:
         super().__init__()
-        self.vocab, self.hidden = vocab, hidden
+        self.vocab, self.hidden, self.softcap = vocab, hidden, float(softcap or 0.0)
         self.declare("weight", (vocab, hidden), ("normal", 0.02), "matrix")
 
     def forward(self, h: torch.Tensor, ctx: Optional[StepContext] = None) -> torch.Tensor:
-        return matmul_nt(h, self.param("weight"), torch.float32, ctx.options if ctx else {})
+        logits = matmul_nt(h, self.param("weight"), torch.float32, ctx.options if ctx else {})
+        if self.softcap > 0.0:
+            K.softcap_rows(logits, self.softcap)
+        return logits

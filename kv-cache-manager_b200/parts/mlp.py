@@ -53,19 +53,35 @@ class GatedMLP(FeedForward):
 
 @FEED_FORWARDS.register("dense_mlp")
 class DenseMLP(FeedForward):
-    """Ungated feed-forward: down( act(x Wu^T) ); act "relu2" = max(z, 0)^2."""
+    """Ungated feed-forward: down( act(x Wu^T) ); act "relu2" = max(z, 0)^2, or "polynorm":
+    a N(z) + b N(z^2) + c N(z^3) + e with the four learned numbers ``act`` = (a, b, c, e), powers taken
+    element by element and N(v) = v / sqrt(mean(v^2) + norm_eps) over a row's ``intermediate`` values (the up
+    product's float32 result goes in; sums and roots are float32)."""
 
-    def __init__(self, hidden: int, intermediate: int, activation: str = "relu2") -> None:
+    def __init__(self, hidden: int, intermediate: int, activation: str = "relu2", norm_eps: float = 1e-6) -> None:
         super().__init__()
-        if activation != "relu2":
-            raise ValueError(f"dense_mlp: activation '{activation}' has no kernel (only 'relu2')")
-        self.hidden, self.intermediate = hidden, intermediate
+        if activation not in ("relu2", "polynorm"):
+            raise ValueError(f"dense_mlp: activation '{activation}' has no kernel (only 'relu2', 'polynorm')")
+        self.hidden, self.intermediate, self.activation, self.norm_eps = hidden, intermediate, activation, float(norm_eps)
         self.up = self.add_child("up", Linear(hidden, intermediate, hidden ** -0.5))
         self.down = self.add_child("down", Linear(intermediate, hidden, intermediate ** -0.5))
+        self._coef = None
+        if activation == "polynorm":
+            self.declare("act", (4,), ("normal", 0.5), "vector")
+
+    def prepare(self, device, dtype) -> None:
+        super().prepare(device, dtype)
+        if self.activation == "polynorm":
+            self._coef = self.param("act").to(device=device, dtype=torch.float32).contiguous()
 
     def forward(self, h: torch.Tensor, ctx: StepContext, out_dtype=None) -> torch.Tensor:
         w = self.up.param("weight")
         M = h.shape[0]
+        if self.activation == "polynorm":
+            z = self.up.forward(h, ctx, out_dtype=torch.float32)
+            act = torch.empty((M, self.intermediate), dtype=h.dtype, device=h.device)
+            K.poly_norm_act(z, self._coef, act, self.norm_eps)
+            return self.down.forward(act, ctx, out_dtype)
         # A handful of rows (decode): the up product applies the activation in its epilogue (the same
         # roundings as the two separate kernels), where `matmul_nt` would take the streaming kernel anyway.
         if (h.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and ctx.options.get("gemm", "auto") in ("auto", "native")

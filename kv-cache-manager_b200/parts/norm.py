@@ -72,3 +72,28 @@ class DynamicTanh(Norm):
             pending = [(pending if pending.dtype == torch.float32 else pending.float(), 1.0)]
         f = self._f32
         K.dyt_norm(x, pending, f["weight"], f["bias"], f["alpha"], out, rows)
+
+
+@NORMS.register("rmsnorm_offset")
+class OffsetRMSNorm(Norm):
+    """RMS norm whose weight is stored as its distance from one: x / sqrt(mean(x^2) + eps) * (1 + w).  The
+    multiplier 1 + w is formed once, in float32 (in 16 bits the sum would lose the weight's low bits), and the
+    statistics are float32.  As a block's norm it is used in pairs by the "sandwich" block (one closes a sublayer,
+    one opens the next: ``kernels.library.norm_post_pre``); ``forward`` is the plain pre-norm, with the row gather
+    of a final norm."""
+
+    def __init__(self, hidden: int, eps: float, init=("normal", 0.1)) -> None:
+        super().__init__()
+        self.hidden, self.eps = hidden, float(eps)
+        self.declare("weight", (hidden,), init, "vector")
+        self.multiplier: Optional[torch.Tensor] = None
+
+    def prepare(self, device, dtype) -> None:
+        super().prepare(device, dtype)
+        self.multiplier = (1.0 + self.param("weight").to(device=device, dtype=torch.float32)).contiguous()
+
+    def forward(self, x: torch.Tensor, pending: Optional[torch.Tensor], out: torch.Tensor,
+                rows: Optional[torch.Tensor] = None) -> None:
+        if pending is not None:
+            K.add_residual(x, pending)
+        K.norm_post_pre(x, None, None, self.multiplier, out, self.eps, rows)
