@@ -389,6 +389,75 @@ def bifatar_work(z, T, ctx, decode):
     }
 
 
+# --compare rivetar: the Rivetar design (attention over a cached latent with a rotated key part; gated linear
+# attention; windowed attention with kept first tokens, a sink and turned values; norms on both sides of every
+# sublayer; PolyNorm feed-forward; a looped span of layers) beside the Llama decoder at equal width, number of
+# layer runs, head count and feed-forward parameter count.
+RIVETAR_SIZES = {
+    "r2048": dict(width=2048, order=("latent_attention", "gla", "attention", "latent_attention"), loop=None, heads=16, kv_heads=4,
+                  dim=128, rot_dim=64, kv_rank=192, q_rank=768, window=1024, keep_first=4, gla_heads=16, llama_ff=4096),
+    "r4096": dict(width=4096, order=("latent_attention", "gla", "attention"), loop=(0, 2, 2), heads=32, kv_heads=8, dim=128,
+                  rot_dim=64, kv_rank=192, q_rank=1536, window=1024, keep_first=4, gla_heads=32, llama_ff=8192),
+}
+
+
+def rivetar_runs(z):
+    """The layer kinds in the order in which they run (a looped span counts every pass)."""
+    order = list(z["order"])
+    if z["loop"]:
+        a, b, times = z["loop"]
+        order = order[:a] + order[a:b] * times + order[b:]
+    return order
+
+
+def rivetar_configs(z):
+    """(Rivetar config, Llama config) of one size.  The ungated feed-forward has two matrices where the gated one
+    has three: its inner size is 1.5 times Llama's.  Llama gets as many layers as Rivetar has layer runs."""
+    from kvcm.config import LlamaConfig, config_from_dict
+    D, H, G, d = z["width"], z["heads"], z["kv_heads"], z["dim"]
+    mlp = {"kind": "dense", "ff": z["llama_ff"] * 3 // 2}
+    layers = []
+    for kind in z["order"]:
+        if kind == "attention":
+            m = {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "scale": d ** -0.5, "rot": {"base": 10000.0, "dims": d // 2},
+                 "mask": {"size": z["window"], "keep_first": z["keep_first"]}}
+        elif kind == "gla":
+            m = {"heads": z["gla_heads"], "dim": d, "vdim": d, "tau": 16.0, "decay_rank": 64}
+        else:
+            m = {"heads": H, "dim": d, "rot_dim": z["rot_dim"], "vdim": d, "kv_rank": z["kv_rank"], "q_rank": z["q_rank"],
+                 "scale": (d + z["rot_dim"]) ** -0.5, "rot": {"base": 10000.0, "dims": z["rot_dim"]}}
+        layers.append({"type": kind, "mixer": m, "mlp": mlp})
+    top = {"architecture": "Rivetar", "vocab": COMPARE_VOCAB, "width": D, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+           "logit_softcap": 30.0, "layers": layers}
+    if z["loop"]:
+        top["loop"] = dict(zip(("start", "stop", "times"), z["loop"]))
+    riv = config_from_dict(top)
+    lla = LlamaConfig(architecture="LlamaForCausalLM", vocab_size=COMPARE_VOCAB, hidden_size=D, intermediate_size=z["llama_ff"],
+                      num_hidden_layers=len(rivetar_runs(z)), num_attention_heads=H, num_key_value_heads=G, head_dim=d,
+                      max_position_embeddings=4096, rope_theta=10000.0, rms_norm_eps=1e-6, tie_word_embeddings=False)
+    return riv, lla
+
+
+def rivetar_work(z, T, ctx, decode):
+    """What the families of one Rivetar step have to do at least: flops, or bytes they must move."""
+    D, H, G, d, W = z["width"], z["heads"], z["kv_heads"], z["dim"], z["window"]
+    runs = rivetar_runs(z)
+    n_win, n_lat, n_gla, L = runs.count("attention"), runs.count("latent_attention"), runs.count("gla"), len(runs)
+    seen_win = T * min(ctx, W + z["keep_first"]) if decode else sum(min(i + 1, W + z["keep_first"]) for i in range(T))
+    seen_all = T * ctx if decode else T * (T + 1) / 2
+    lat = z["kv_rank"] + z["rot_dim"]
+    state = z["gla_heads"] * d * d
+    ff = z["llama_ff"] * 3 // 2
+    return {
+        "attention": dict(flops=4.0 * H * (d * seen_win * n_win + lat * seen_all * n_lat),
+                          bytes=2.0 * (2 * G * d * T * min(ctx, W) * n_win + lat * T * ctx * n_lat) if decode else None),
+        "state_scan": dict(flops=T * 4.0 * state * n_gla, bytes=8.0 * T * state * n_gla if decode else None),
+        "feed_forward": dict(flops=2.0 * T * 2 * ff * D * L, bytes=2.0 * 2 * ff * D * L if decode else None),
+        "norm_post_pre": dict(flops=None, bytes=T * D * (4.0 * 3 + 2.0) * 2 * L),
+        "poly_norm_act": dict(flops=None, bytes=T * ff * (4.0 + 2.0) * L),
+    }
+
+
 def compare_main(args) -> int:
     import torch
     from kvcm.config import EngineConfig, KVManagerConfig, SchedulerConfig
@@ -396,8 +465,9 @@ def compare_main(args) -> int:
     from kvcm.weights import random_tensors
     pk = peaks()
     first = args.compare
-    sizes, configs, first_work = ((BIFATAR_SIZES, bifatar_configs, bifatar_work) if first == "bifatar"
-                                  else (COMPARE_SIZES, compare_configs, tolanex_work))
+    sizes, configs, first_work = {"bifatar": (BIFATAR_SIZES, bifatar_configs, bifatar_work),
+                                  "rivetar": (RIVETAR_SIZES, rivetar_configs, rivetar_work),
+                                  "tolanex": (COMPARE_SIZES, compare_configs, tolanex_work)}[first]
     out = {"compare": f"{first} beside llama at equal width, depth and (active) feed-forward size", "dtype": "bf16",
            "data": "synthetic: random weights, uniform random token ids", "peaks": pk, "sizes": {}}
     steps, warmup = min(args.steps, 200), max(args.warmup, 3)
@@ -406,6 +476,8 @@ def compare_main(args) -> int:
             continue
         if first == "bifatar":
             z = dict(z, layers=len(z["order"]), top=1, ff=z["llama_ff"], shared=0)      # the keys llama_work reads
+        elif first == "rivetar":
+            z = dict(z, layers=len(rivetar_runs(z)), top=1, ff=z["llama_ff"], shared=0)
         res = {}
         for arch, cfg in zip((first, "llama"), configs(z)):
             tensors = dict(random_tensors(cfg, 0, torch.bfloat16, device="cuda:0"))
@@ -560,8 +632,8 @@ def main() -> int:
                          "'native' this engine's kernels only, 'library' the library wherever it can stand")
     ap.add_argument("--only", default="all", choices=["all", "prefill"],
                     help="'prefill': run only the 2,048-token prefill step and print its numbers (for profiling)")
-    ap.add_argument("--compare", default="", choices=["", "tolanex", "bifatar"],
-                    help="'tolanex' | 'bifatar': instead of the default workload, prefill and decode of that design beside "
+    ap.add_argument("--compare", default="", choices=["", "tolanex", "bifatar", "rivetar"],
+                    help="'tolanex' | 'bifatar' | 'rivetar': instead of the default workload, prefill and decode of that design beside "
                          "the Llama decoder at equal sizes, with device time per kernel family")
     ap.add_argument("--size", default="all", choices=["all"] + sorted(COMPARE_SIZES) + sorted(BIFATAR_SIZES),
                     help="with --compare: one size only")

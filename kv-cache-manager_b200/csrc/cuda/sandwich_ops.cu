@@ -207,7 +207,7 @@ static int launch_norm_post_pre(float* x, const float* y, const float* wb, const
   if ((y && !wb) || (out && !wn) || (!y && !out) || (rows_idx && !out)) return KVCM_ERR_UNSUPPORTED;
   const size_t smem = size_t(H) * sizeof(float);
   if (smem > 200 * 1024) return KVCM_ERR_UNSUPPORTED;
-  if (smem > 48 * 1024) {
+  if (smem > 40 * 1024) {                               // (the kernel's static shared memory counts against the 48 KB too)
     const cudaError_t e = cudaFuncSetAttribute(norm_post_pre_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     if (e != cudaSuccess) return int(e);
   }
@@ -226,7 +226,7 @@ static int launch_poly_norm(const float* z, int ldz, const float* coef, void* ou
   if (rows == 0) return 0;
   const size_t smem = size_t(F) * sizeof(float);
   if (smem > 200 * 1024) return KVCM_ERR_UNSUPPORTED;
-  if (smem > 48 * 1024) {
+  if (smem > 40 * 1024) {                               // (the kernel's static shared memory counts against the 48 KB too)
     const cudaError_t e = cudaFuncSetAttribute(poly_norm_act_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     if (e != cudaSuccess) return int(e);
   }

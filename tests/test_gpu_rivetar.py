@@ -216,8 +216,11 @@ def test_one_layer_alone(tmp_path, layer, top):
 ], ids=["attn128_keep", "attn128_window", "attn64_48_keep70", "attn20heads", "gla128", "latent128", "latent256"])
 def test_mixers_at_the_sizes_of_the_fast_kernels(tmp_path, layer, dtype):
     """Head and state sizes that take the tensor-core attention kernels and the wide forms of the recurrence
-    kernel, in a prompt of three portions and 70 decoded tokens, beside a second request."""
+    kernel, in a prompt of three portions and 70 decoded tokens, beside a second request.  (A request's first
+    position is left out for the gla layer in bfloat16: its state is k v^T there, the head's output (q.k) v, and
+    the norm over it keeps only the sign of q.k, which rounding decides when q.k is near zero.)"""
     folder = one_layer_model(tmp_path, layer, dtype, width=256, vocab=200)
+    skip = 1 if layer["type"] == "gla" and dtype == "bfloat16" else 0
     cfg, w = RM.read_model(folder)
     toks, other = helpers.random_tokens(420, 200, 3), helpers.random_tokens(150, 200, 4)
     ref, ref2 = P.forward(cfg, w, toks), P.forward(cfg, w, other)
@@ -235,8 +238,8 @@ def test_mixers_at_the_sizes_of_the_fast_kernels(tmp_path, layer, dtype):
         outs.append(out[:1])
         if k < 50:
             o2.append(out[1:])
-    close(torch.cat(outs), ref, dtype, "first request")
-    close(torch.cat(o2), ref2, dtype, "second request")
+    close(torch.cat(outs)[skip:], ref[skip:], dtype, "first request")
+    close(torch.cat(o2)[skip:], ref2[skip:len(torch.cat(o2))], dtype, "second request")
 
 
 # ------------------------------------------------------------ one key that carries all the weight
