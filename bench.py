@@ -635,7 +635,7 @@ def main() -> int:
     ap.add_argument("--compare", default="", choices=["", "tolanex", "bifatar", "rivetar"],
                     help="'tolanex' | 'bifatar' | 'rivetar': instead of the default workload, prefill and decode of that design beside "
                          "the Llama decoder at equal sizes, with device time per kernel family")
-    ap.add_argument("--size", default="all", choices=["all"] + sorted(COMPARE_SIZES) + sorted(BIFATAR_SIZES),
+    ap.add_argument("--size", default="all", choices=["all"] + sorted(COMPARE_SIZES) + sorted(BIFATAR_SIZES) + sorted(RIVETAR_SIZES),
                     help="with --compare: one size only")
     args = ap.parse_args()
 

@@ -82,6 +82,65 @@ norm_post_pre_kernel(float* __restrict__ x, const float* __restrict__ y, const f
   }
 }
 
+// Four values a thread and access (H % 4 == 0 and 16-byte aligned rows); as many threads as a row has float4s, at most 512.
+__device__ __forceinline__ void st4(float* p, float a, float b, float c, float d) {
+  *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void st4(bf16* p, float a, float b, float c, float d) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+  uint2 u;
+  u.x = *reinterpret_cast<const unsigned*>(&lo);
+  u.y = *reinterpret_cast<const unsigned*>(&hi);
+  *reinterpret_cast<uint2*>(p) = u;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(512)
+norm_post_pre_vec_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ wb,
+                         const float* __restrict__ wn, T* __restrict__ out, const int* __restrict__ rows, int H, float eps) {
+  extern __shared__ __align__(16) float row[];
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = rows ? rows[blockIdx.x] : blockIdx.x;
+  float* xr = x + size_t(r) * H;
+  float s2 = 0.f;
+  if (y) {
+    const float* yr = y + size_t(r) * H;
+    float ss = 0.f;
+    for (int i = 4 * threadIdx.x; i < H; i += 4 * blockDim.x) {
+      const float4 v = *reinterpret_cast<const float4*>(yr + i);
+      *reinterpret_cast<float4*>(row + i) = v;
+      ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.f / sqrtf(ss / float(H) + eps);
+    for (int i = 4 * threadIdx.x; i < H; i += 4 * blockDim.x) {
+      const float4 xv = *reinterpret_cast<const float4*>(xr + i), w = *reinterpret_cast<const float4*>(wb + i);
+      float4 v = *reinterpret_cast<const float4*>(row + i);
+      v.x = xv.x + w.x * (v.x * inv); v.y = xv.y + w.y * (v.y * inv);
+      v.z = xv.z + w.z * (v.z * inv); v.w = xv.w + w.w * (v.w * inv);
+      *reinterpret_cast<float4*>(row + i) = v;
+      if (!rows) *reinterpret_cast<float4*>(xr + i) = v;
+      s2 = fmaf(v.x, v.x, s2); s2 = fmaf(v.y, v.y, s2); s2 = fmaf(v.z, v.z, s2); s2 = fmaf(v.w, v.w, s2);
+    }
+    if (!out) return;
+  } else {
+    for (int i = 4 * threadIdx.x; i < H; i += 4 * blockDim.x) {
+      const float4 v = *reinterpret_cast<const float4*>(xr + i);
+      *reinterpret_cast<float4*>(row + i) = v;
+      s2 = fmaf(v.x, v.x, s2); s2 = fmaf(v.y, v.y, s2); s2 = fmaf(v.z, v.z, s2); s2 = fmaf(v.w, v.w, s2);
+    }
+  }
+  s2 = block_sum(s2, scratch);
+  const float inv2 = 1.f / sqrtf(s2 / float(H) + eps);
+  T* o = out + size_t(blockIdx.x) * H;
+  for (int i = 4 * threadIdx.x; i < H; i += 4 * blockDim.x) {
+    const float4 v = *reinterpret_cast<const float4*>(row + i), w = *reinterpret_cast<const float4*>(wn + i);
+    st4(o + i, w.x * (v.x * inv2), w.y * (v.y * inv2), w.z * (v.z * inv2), w.w * (v.w * inv2));
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 poly_norm_act_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ coef, T* __restrict__ out, int F,
@@ -110,6 +169,43 @@ poly_norm_act_kernel(const float* __restrict__ z, int ldz, const float* __restri
   for (int i = threadIdx.x; i < F; i += blockDim.x) {
     const float v = row[i], v2 = v * v;
     stf(o + i, a * v + b * v2 + c * (v2 * v) + e);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(512)
+poly_norm_act_vec_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ coef, T* __restrict__ out, int F,
+                         float eps) {
+  extern __shared__ __align__(16) float row[];
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const float* zr = z + size_t(blockIdx.x) * ldz;
+  float s2 = 0.f, s4 = 0.f, s6 = 0.f;
+  for (int i = 4 * threadIdx.x; i < F; i += 4 * blockDim.x) {
+    const float4 q = *reinterpret_cast<const float4*>(zr + i);
+    *reinterpret_cast<float4*>(row + i) = q;
+    const float e[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float v2 = e[k] * e[k], v3 = v2 * e[k];
+      s2 += v2;
+      s4 = fmaf(v2, v2, s4);
+      s6 = fmaf(v3, v3, s6);
+    }
+  }
+  s2 = block_sum(s2, scratch);
+  s4 = block_sum(s4, scratch);
+  s6 = block_sum(s6, scratch);
+  const float n = float(F);
+  const float a = coef[0] / sqrtf(s2 / n + eps), b = coef[1] / sqrtf(s4 / n + eps), c = coef[2] / sqrtf(s6 / n + eps);
+  const float e0 = coef[3];
+  T* o = out + size_t(blockIdx.x) * F;
+  for (int i = 4 * threadIdx.x; i < F; i += 4 * blockDim.x) {
+    const float4 q = *reinterpret_cast<const float4*>(row + i);
+    const float x2 = q.x * q.x, y2 = q.y * q.y, z2 = q.z * q.z, w2 = q.w * q.w;
+    st4(o + i, a * q.x + b * x2 + c * (x2 * q.x) + e0, a * q.y + b * y2 + c * (y2 * q.y) + e0,
+        a * q.z + b * z2 + c * (z2 * q.z) + e0, a * q.w + b * w2 + c * (w2 * q.w) + e0);
   }
 }
 
@@ -188,6 +284,16 @@ gla_prepare_kernel(float* __restrict__ qkv, int channels, int q_base, int n_q, f
 
 using namespace kvcm;
 
+// Threads of a four-values-a-thread kernel over rows of n values: one float4 each, between 64 and 512.
+static int vec_threads(int n) {
+  const int t = ((n / 4) + 31) / 32 * 32;
+  return t < 64 ? 64 : (t > 512 ? 512 : t);
+}
+template <typename... P>
+static bool aligned16(const P*... p) {
+  return (((reinterpret_cast<uintptr_t>(p)) | ...) & 15) == 0;
+}
+
 #define KVCM_EMBED_SCALED_ARGS const int *ids, const void *table, float *x, float *keep, int rows, int H, int vocab, float scale, void *stream
 KVCM_API int kvcm_embed_scaled_f32(KVCM_EMBED_SCALED_ARGS) {
   if (rows == 0) return 0;
@@ -207,6 +313,13 @@ static int launch_norm_post_pre(float* x, const float* y, const float* wb, const
   if ((y && !wb) || (out && !wn) || (!y && !out) || (rows_idx && !out)) return KVCM_ERR_UNSUPPORTED;
   const size_t smem = size_t(H) * sizeof(float);
   if (smem > 200 * 1024) return KVCM_ERR_UNSUPPORTED;
+  if (H % 4 == 0 && aligned16(x, y, wb, wn, out)) {
+    if (smem > 40 * 1024) {
+      const cudaError_t e = cudaFuncSetAttribute(norm_post_pre_vec_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+      if (e != cudaSuccess) return int(e);
+    }
+    return pdl_launch(norm_post_pre_vec_kernel<T>, dim3(rows), dim3(vec_threads(H)), smem, s, x, y, wb, wn, (T*)out, rows_idx, H, eps);
+  }
   if (smem > 40 * 1024) {                               // (the kernel's static shared memory counts against the 48 KB too)
     const cudaError_t e = cudaFuncSetAttribute(norm_post_pre_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     if (e != cudaSuccess) return int(e);
@@ -226,6 +339,13 @@ static int launch_poly_norm(const float* z, int ldz, const float* coef, void* ou
   if (rows == 0) return 0;
   const size_t smem = size_t(F) * sizeof(float);
   if (smem > 200 * 1024) return KVCM_ERR_UNSUPPORTED;
+  if (F % 4 == 0 && ldz % 4 == 0 && aligned16(z, out)) {
+    if (smem > 40 * 1024) {
+      const cudaError_t e = cudaFuncSetAttribute(poly_norm_act_vec_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+      if (e != cudaSuccess) return int(e);
+    }
+    return pdl_launch(poly_norm_act_vec_kernel<T>, dim3(rows), dim3(vec_threads(F)), smem, s, z, ldz, coef, (T*)out, F, eps);
+  }
   if (smem > 40 * 1024) {                               // (the kernel's static shared memory counts against the 48 KB too)
     const cudaError_t e = cudaFuncSetAttribute(poly_norm_act_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     if (e != cudaSuccess) return int(e);

@@ -248,6 +248,28 @@ class PositionEncoding(Part):
     pass
 
 
+class ClosingNorm:
+    """A sublayer's float32 output ``y`` that is still to be added to the stream through an RMS norm:
+    x += multiplier * y / sqrt(mean(y^2) + eps).  A block may hand this on as its pending value so that the
+    reader of the stream applies it in the same kernel as its own opening norm."""
+    __slots__ = ("y", "multiplier", "eps")
+
+    def __init__(self, y: torch.Tensor, multiplier: torch.Tensor, eps: float) -> None:
+        self.y, self.multiplier, self.eps = y, multiplier, float(eps)
+
+
+def settle(x: torch.Tensor, pending) -> None:
+    """Brings the float32 stream ``x`` up to date with what the layer before left pending: nothing, a tensor
+    to add, or a ``ClosingNorm``."""
+    from ..kernels import library as K
+    if pending is None:
+        return
+    if isinstance(pending, ClosingNorm):
+        K.norm_post_pre(x, pending.y, pending.multiplier, None, None, pending.eps)
+    else:
+        K.add_residual(x, pending)
+
+
 class StreamPart(Part):
     """A part between two layers: ``forward(x, pending, ctx, arg) -> (x', pending')`` takes the float32
     residual stream (and what the layer before left pending) and returns the stream the next layer reads."""

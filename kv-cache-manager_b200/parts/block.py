@@ -10,7 +10,7 @@ from typing import Optional
 import torch
 
 from ..kernels import library as K
-from .base import BLOCKS, Block, FeedForward, Mixer, Norm, SiteCache, StepContext
+from .base import BLOCKS, Block, ClosingNorm, FeedForward, Mixer, Norm, SiteCache, StepContext, settle
 
 
 @BLOCKS.register("pre_norm")
@@ -93,9 +93,11 @@ class ParallelBlock(Block):
 class SandwichBlock(Block):
     """Every sublayer normalised on both sides: x += norm1b(mixer(norm1(x))); x += norm2b(ffn(norm2(x))).  The four
     norms expose ``multiplier`` (float32 [hidden]) and ``eps`` ("rmsnorm_offset").  The sublayers return float32; the
-    norm that closes one sublayer and the norm that opens the next are one kernel (the closing norm of the
-    layer's last sublayer runs alone, so that the stream is complete when the layer ends; ``fuse`` off: every
-    norm is a launch of its own).  ``ffn`` may be None: a layer of a mixer only."""
+    norm that closes one sublayer and the norm that opens the next are one kernel, also across layers: the
+    closing norm of a layer's last sublayer is handed on as a ``ClosingNorm`` and applied by whatever reads the
+    stream next (the next sandwich block's opening norm, the final norm, or a part between layers through
+    ``settle``).  ``fuse`` off: every norm is a launch of its own and the stream is complete when the layer ends.
+    ``ffn`` may be None: a layer of a mixer only."""
 
     def __init__(self, norm1: Norm, mixer: Mixer, norm1b: Norm, norm2: Optional[Norm] = None,
                  ffn: Optional[FeedForward] = None, norm2b: Optional[Norm] = None) -> None:
@@ -109,21 +111,28 @@ class SandwichBlock(Block):
         if not ((self.norm2 is None) == (self.ffn is None) == (self.norm2b is None)):
             raise ValueError("sandwich block: a feed-forward and its two norms come together")
 
-    def forward(self, x: torch.Tensor, pending: Optional[torch.Tensor], ctx: StepContext,
-                site: SiteCache) -> Optional[torch.Tensor]:
-        if pending is not None:
-            K.add_residual(x, pending)
+    def forward(self, x: torch.Tensor, pending, ctx: StepContext, site: SiteCache):
+        fuse = ctx.options.get("fuse", True)
         h = torch.empty(x.shape, dtype=ctx.dtype, device=x.device)
-        K.norm_post_pre(x, None, None, self.norm1.multiplier, h, self.norm1.eps)
+        if isinstance(pending, ClosingNorm) and pending.eps == self.norm1.eps:
+            K.norm_post_pre(x, pending.y, pending.multiplier, self.norm1.multiplier, h, self.norm1.eps)
+        else:
+            settle(x, pending)
+            K.norm_post_pre(x, None, None, self.norm1.multiplier, h, self.norm1.eps)
         y = self.mixer.forward(h, ctx, site)
         if self.ffn is None:
-            K.norm_post_pre(x, y, self.norm1b.multiplier, None, None, self.norm1b.eps)
-            return None
-        if ctx.options.get("fuse", True) and self.norm1b.eps == self.norm2.eps:
+            return self._close(x, y, self.norm1b, fuse)
+        if fuse and self.norm1b.eps == self.norm2.eps:
             K.norm_post_pre(x, y, self.norm1b.multiplier, self.norm2.multiplier, h, self.norm2.eps)
         else:
             K.norm_post_pre(x, y, self.norm1b.multiplier, None, None, self.norm1b.eps)
             K.norm_post_pre(x, None, None, self.norm2.multiplier, h, self.norm2.eps)
         y = self.ffn.forward(h, ctx, out_dtype=torch.float32)
-        K.norm_post_pre(x, y, self.norm2b.multiplier, None, None, self.norm2b.eps)
+        return self._close(x, y, self.norm2b, fuse)
+
+    @staticmethod
+    def _close(x: torch.Tensor, y: torch.Tensor, norm: Norm, fuse: bool):
+        if fuse:
+            return ClosingNorm(y, norm.multiplier, norm.eps)
+        K.norm_post_pre(x, y, norm.multiplier, None, None, norm.eps)
         return None

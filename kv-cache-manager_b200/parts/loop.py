@@ -14,7 +14,7 @@ from __future__ import annotations
 import torch
 
 from ..kernels import library as K
-from .base import StepContext, StreamPart
+from .base import StepContext, StreamPart, settle
 from .linear import Linear
 
 
@@ -32,8 +32,7 @@ class LoopEntry(StreamPart):
 
     def forward(self, x: torch.Tensor, pending, ctx: StepContext, arg=None):
         t = int(arg or 0)
-        if pending is not None:
-            K.add_residual(x, pending)
+        settle(x, pending)
         both = torch.empty((x.shape[0], 2 * self.hidden), dtype=ctx.dtype, device=x.device)
         K.concat_cast(x, ctx.shared[self.source], both)
         y = self.inp.forward(both, ctx, out_dtype=torch.float32)

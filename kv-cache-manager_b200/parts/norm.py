@@ -11,7 +11,7 @@ from typing import Optional
 import torch
 
 from ..kernels import library as K
-from .base import NORMS, Norm
+from .base import NORMS, ClosingNorm, Norm, settle
 
 
 @NORMS.register("rmsnorm")
@@ -94,6 +94,8 @@ class OffsetRMSNorm(Norm):
 
     def forward(self, x: torch.Tensor, pending: Optional[torch.Tensor], out: torch.Tensor,
                 rows: Optional[torch.Tensor] = None) -> None:
-        if pending is not None:
-            K.add_residual(x, pending)
+        if isinstance(pending, ClosingNorm) and pending.eps == self.eps:
+            K.norm_post_pre(x, pending.y, pending.multiplier, self.multiplier, out, self.eps, rows)
+            return
+        settle(x, pending)
         K.norm_post_pre(x, None, None, self.multiplier, out, self.eps, rows)
