@@ -1,5 +1,6 @@
 // Causal prefill attention over the paged cache on the fifth-generation tensor cores (head_dim 64
-// or 128).
+// or 128; 256 when keys and values are the same pages, as they are for attention over a cached latent:
+// a tile is then loaded once and read by both products, in a ring of three stages).
 //
 // One block per (128 query rows of a request, query head).  Per tile of 64 keys:
 //     S = Q K^T  (tcgen05.mma, M 128 x N 64, accumulator in tensor memory, two buffers)
@@ -20,7 +21,9 @@
 // mbarriers; warps 2-5 do the softmax and the output.  At head_dim 64 two blocks share an SM (112 KB
 // of shared memory and 256 columns of tensor memory each); at 128 a block takes 192 KB.  Keys come from the pages, the portion's own
 // included (they were written before), so a portion may start anywhere in a request; masks: key <=
-// row's position, key > position - window, key < end of the request's computed part.  Scores are
+// row's position, key > position - window (or key < keep_first: a window that keeps a request's first
+// keys; the tiles that hold them are walked before the window's own), key < end of the request's computed
+// part.  Scores are
 // scaled in float; softmax by exp2 with log2(e) folded into the scale; probabilities are rounded
 // to bfloat16 for the product with V, their sums stay float.
 // Every wait on an mbarrier is bounded; when one runs out the block records it
@@ -35,10 +38,11 @@ namespace kvcm {
 constexpr int kFaThreads = 192;
 constexpr int kFaRows = 128;                 // query rows per block
 constexpr int kFaKeys = 64;                  // keys per tile
-constexpr int kFaStages = 4;                 // K/V tiles in flight
+constexpr int kFaStagesMax = 4;              // K/V tiles in flight (three at head_dim 256)
 constexpr int kFaTileBytes = 128 * 128;      // [128 rows][64 bf16]: a 64-wide block of Q, a buffer of P
 constexpr int kFaKvBlock = kFaKeys * 128;    // [64 keys][64 bf16]: a 64-wide block of a stage of K or of V
-constexpr int kFaTmemCols = 256;             // S: two buffers, columns 0..63 and 64..127; O: columns 128..(128 + head_dim)
+// tensor memory: S in two buffers, columns 0..63 and 64..127; O in columns 128..(128 + head_dim); 256 columns
+// (512 at head_dim 256)
 // head_dim 64 or 128.  Operands wider than 64 elements are kept as blocks of 64 (one 128-byte
 // swizzled row each): Q [HD/64][128 rows][64], a stage of K or V [HD/64][64 keys][64]; the
 // products step through the blocks (S over head_dim) or write 64 columns of O per block of V.
@@ -52,6 +56,7 @@ struct PrefillTcParams {
   const int* tile_seq; const int* tile_q0;                 // tiles of 64 rows; a block takes an even one and its successor
   const int* seq_q_start; const int* seq_q_len; const int* seq_ctx_len;
   int nh, nkv, block_size, window;
+  int keep_first;                   // with a window: keys below this stay visible to every later row (0: none)
   float scale_log2;                 // what a score is multiplied by on its way into exp2
   float cap_pre;                    // > 0: scores are capped, s <- tanh(s * cap_pre) first (cap_pre = scale / cap and
                                     // scale_log2 = cap * log2(e))
@@ -82,18 +87,21 @@ __device__ __forceinline__ float fa_max3(float a, float b, float c) {
   return d;
 }
 
-template <int HD>
+template <int HD, bool SHARED>
 __global__ void __launch_bounds__(HD == 64 ? 256 : kFaThreads, HD == 64 ? 2 : 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, PrefillTcParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   constexpr int KB = HD / 64;                                  // 64-wide blocks of head_dim
   constexpr int kFaKvBytes = KB * kFaKvBlock;                  // a stage of K or of V
+  constexpr int kFaStages = HD == 256 ? 3 : 4;
+  constexpr int kFaTmemCols = HD == 256 ? 512 : 256;
+  static_assert(HD != 256 || SHARED, "head_dim 256 needs keys and values in the same pages");
   unsigned char* q_s = smem_raw;                               // [KB][128 rows][64]             16 KB x KB
   unsigned char* k_s = q_s + KB * kFaTileBytes;                // [stages][KB][64 keys][64]      32 KB x KB
-  unsigned char* v_s = k_s + kFaStages * kFaKvBytes;           // [stages][KB][64 keys][64]      32 KB x KB
+  unsigned char* v_s = SHARED ? k_s : k_s + kFaStages * kFaKvBytes;   // [stages][KB][64 keys][64]; the keys' tiles when SHARED
   unsigned char* p_s = v_s + kFaStages * kFaKvBytes;           // [2][128 rows][64 keys]         32 KB
-  __shared__ __align__(8) uint64_t q_full, kv_full[kFaStages], kv_empty[kFaStages], s_full[2], s_free[2], p_full[2],
+  __shared__ __align__(8) uint64_t q_full, kv_full[kFaStagesMax], kv_empty[kFaStagesMax], s_full[2], s_free[2], p_full[2],
       p_free[2], o_full;
   __shared__ uint32_t tmem_base;
   __shared__ volatile int abort_flag;
@@ -115,7 +123,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int pos0 = ctx - q_len + q0;                           // position of the block's first row
   const int hi = pos0 + rows_here;                             // keys [lo, hi) matter to the block
   const int lo = (p.window > 0 && pos0 + 1 > p.window) ? pos0 + 1 - p.window : 0;
-  const int j0 = lo / kFaKeys, n_tiles = (hi - 1) / kFaKeys - j0 + 1;
+  const int j0 = lo / kFaKeys;
+  // Kept first keys below the window's own tiles: n_keep tiles from key 0 come first, then tiles j0, j0 + 1, ...
+  const int keep = (p.window > 0 && lo > 0 && p.keep_first > 0) ? min(p.keep_first, lo) : 0;
+  const int n_keep = min((keep + kFaKeys - 1) / kFaKeys, j0);
+  const int n_tiles = n_keep + (hi - 1) / kFaKeys - j0 + 1;
+  auto key_tile = [&](int n) { return n < n_keep ? n : j0 + n - n_keep; };
   const int kvh = head / (p.nh / p.nkv);
 
   if (threadIdx.x == 0) {
@@ -134,7 +147,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   }
   // The K/V ring starts as zeros: pages beyond the request's last key are not loaded, and what a
   // slot holds there is multiplied by probability zero, so it must be finite.
-  for (int i = threadIdx.x; i < 2 * kFaStages * kFaKvBytes / 16; i += kFaThreads)
+  for (int i = threadIdx.x; i < (SHARED ? 1 : 2) * kFaStages * kFaKvBytes / 16; i += kFaThreads)
     reinterpret_cast<uint4*>(k_s)[i] = make_uint4(0u, 0u, 0u, 0u);
   asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   if (warp == 1) {
@@ -171,11 +184,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
-      const int key0 = (j0 + n) * kFaKeys;
+      const int key0 = key_tile(n) * kFaKeys;
       const int count = min(per_tile, (hi - key0 + box - 1) / box);             // boxes that hold keys below hi
       if (lane == 0)
         asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n"
-                     ::"r"(tc5::s32(&kv_full[s])), "r"(2 * KB * count * box * 128) : "memory");
+                     ::"r"(tc5::s32(&kv_full[s])), "r"((SHARED ? 1 : 2) * KB * count * box * 128) : "memory");
       __syncwarp();
       for (int i = lane; i < count; i += 32) {
         const int key = key0 + i * box;
@@ -183,7 +196,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int row = (page * p.nkv + kvh) * B + key % B;
         for (int kb = 0; kb < KB; ++kb) {
           tc5::tma_load_2d(k_s + s * kFaKvBytes + kb * kFaKvBlock + i * box * 128, &map_k, &kv_full[s], kb * 64, row);
-          tc5::tma_load_2d(v_s + s * kFaKvBytes + kb * kFaKvBlock + i * box * 128, &map_v, &kv_full[s], kb * 64, row);
+          if (!SHARED)
+            tc5::tma_load_2d(v_s + s * kFaKvBytes + kb * kFaKvBlock + i * box * 128, &map_v, &kv_full[s], kb * 64, row);
         }
       }
     }
@@ -255,12 +269,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[c][i] = __float_as_uint(fa_tanh(__uint_as_float(v[c][i]) * p.cap_pre));
       }
-      const int key0 = (j0 + n) * kFaKeys;
-      // the keys of this tile that the row may see: [a, b) relative to the tile
+      const int key0 = key_tile(n) * kFaKeys;
+      // the keys of this tile that the row may see: [a, b) relative to the tile, and with kept first keys [0, kk) too
       const int a = max(first, lo) - key0, b = min(pos + 1, hi) - key0;
+      const int kk = (p.window > 0 ? p.keep_first : 0) - key0;
       // Masks are needed only where the tile touches the diagonal, the window's edge or the end of
       // the keys; for every other tile (most of a long prompt) there is none.
-      const bool full = key0 + kFaKeys - 1 <= pos0 && (p.window <= 0 || key0 >= pos0 + kFaRows - p.window);
+      const bool full = key0 + kFaKeys - 1 <= pos0 && (p.window <= 0 || key0 >= pos0 + kFaRows - p.window || kk >= kFaKeys);
       float mx[2] = {-INFINITY, -INFINITY};
       if (full) {
         // eight chains of three-input maxima, four steps deep, instead of two chains of 32
@@ -282,7 +297,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const int t = c * 32 + i;
-            mx[c] = (t >= a && t < b) ? fmaxf(mx[c], __uint_as_float(v[c][i])) : mx[c];
+            mx[c] = ((t >= a || t < kk) && t < b) ? fmaxf(mx[c], __uint_as_float(v[c][i])) : mx[c];
           }
       }
       const float m_tile = fmaxf(mx[0], mx[1]) * p.scale_log2;
@@ -339,8 +354,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
             const int t = c * 32 + i;
-            const float p0 = (t >= a && t < b) ? fa_exp2(__uint_as_float(v[c][i]) * p.scale_log2 - m_use) : 0.f;
-            const float p1 = (t + 1 >= a && t + 1 < b) ? fa_exp2(__uint_as_float(v[c][i + 1]) * p.scale_log2 - m_use) : 0.f;
+            const float p0 = ((t >= a || t < kk) && t < b) ? fa_exp2(__uint_as_float(v[c][i]) * p.scale_log2 - m_use) : 0.f;
+            const float p1 = ((t + 1 >= a || t + 1 < kk) && t + 1 < b) ? fa_exp2(__uint_as_float(v[c][i + 1]) * p.scale_log2 - m_use) : 0.f;
             sum[c] += p0 + p1;
             const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
             packed[i / 2] = *reinterpret_cast<const uint32_t*>(&h);
@@ -408,11 +423,29 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
 using namespace kvcm;
 
-// 1 if the tcgen05 prefill kernel takes these sizes: head_dim 64 or 128; pages of 8, 16, 32 or 64 keys, or a
-// multiple of 64 (up to 256, the largest box).
-KVCM_API int kvcm_attention_tcgen05_supports(int hd, int block_size) {
-  if ((hd != 64 && hd != 128) || block_size < 8 || block_size > 256) return 0;
+// 1 if the tcgen05 prefill kernel takes these sizes: head_dim 64 or 128, or 256 when keys and values are the same
+// pages (`shared_kv`); pages of 8, 16, 32 or 64 keys, or a multiple of 64 (up to 256, the largest box).
+KVCM_API int kvcm_attention_tcgen05_supports_kv(int hd, int block_size, int shared_kv) {
+  if ((hd != 64 && hd != 128 && !(hd == 256 && shared_kv)) || block_size < 8 || block_size > 256) return 0;
   return block_size <= kFaKeys ? (kFaKeys % block_size) == 0 && (block_size % 8) == 0 : (block_size % kFaKeys) == 0;
+}
+KVCM_API int kvcm_attention_tcgen05_supports(int hd, int block_size) {
+  return kvcm_attention_tcgen05_supports_kv(hd, block_size, 0);
+}
+
+template <int HD, bool SHARED>
+static int launch_prefill_tc(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const PrefillTcParams& p,
+                             dim3 grid, cudaStream_t s) {
+  constexpr int KB = HD / 64, stages = HD == 256 ? 3 : 4;
+  // 112 KB at head_dim 64 (two blocks fit an SM exactly), 192 KB at 128 and at 256
+  constexpr size_t smem = size_t(KB + 2) * kFaTileBytes + size_t(SHARED ? 1 : 2) * stages * KB * kFaKvBlock;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD, SHARED>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (e != cudaSuccess) return int(e);
+    configured = true;
+  }
+  return pdl_launch(attn_prefill_tc_kernel<HD, SHARED>, grid, dim3(kFaThreads), smem, s, mq, mk, mv, p);
 }
 
 // q: [total_rows, >= nh*64] rows `q_stride` elements apart (16-byte aligned, q_stride % 8 == 0); the
@@ -423,10 +456,11 @@ KVCM_API int kvcm_attention_prefill_tcgen05_bf16(const void* q, int q_stride, in
                                                  const int* block_tables, int max_blocks, const int* tile_seq,
                                                  const int* tile_q0, const int* seq_q_start, const int* seq_q_len,
                                                  const int* seq_ctx_len, int tiles, int nh, int nkv, int hd,
-                                                 int block_size, float scale, int window, float softcap, const float* sink,
-                                                 void* stream) {
+                                                 int block_size, float scale, int window, int keep_first, float softcap,
+                                                 const float* sink, void* stream) {
   if (tiles == 0) return 0;
-  if (!kvcm_attention_tcgen05_supports(hd, block_size) || nkv <= 0 || nh % nkv) return KVCM_ERR_UNSUPPORTED;
+  if (!kvcm_attention_tcgen05_supports_kv(hd, block_size, k_cache == v_cache) || nkv <= 0 || nh % nkv || keep_first < 0)
+    return KVCM_ERR_UNSUPPORTED;
   if ((q_stride % 8) || (out_stride % 8) || (reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(out) & 15) ||
       (reinterpret_cast<uintptr_t>(k_cache) & 15) || (reinterpret_cast<uintptr_t>(v_cache) & 15))
     return KVCM_ERR_UNSUPPORTED;
@@ -444,30 +478,15 @@ KVCM_API int kvcm_attention_prefill_tcgen05_bf16(const void* q, int q_stride, in
   p.block_tables = block_tables; p.max_blocks = max_blocks; p.tile_seq = tile_seq; p.tile_q0 = tile_q0;
   p.seq_q_start = seq_q_start; p.seq_q_len = seq_q_len; p.seq_ctx_len = seq_ctx_len;
   p.nh = nh; p.nkv = nkv; p.block_size = block_size; p.window = window;
+  p.keep_first = window > 0 ? keep_first : 0;
   p.scale_log2 = (softcap > 0.f ? softcap : scale) * 1.4426950408889634f;
   p.cap_pre = softcap > 0.f ? scale / softcap : 0.f;
   p.sink = sink;
-  const int KB = hd / 64;
-  // 112 KB at head_dim 64 (two blocks fit an SM exactly), 192 KB at 128
-  const size_t smem = size_t(KB + 2) * kFaTileBytes + size_t(2) * kFaStages * KB * kFaKvBlock;
-  const dim3 grid(nh, tiles), block(kFaThreads);
+  const dim3 grid(nh, tiles);
   cudaStream_t s = (cudaStream_t)stream;
-  if (hd == 64) {
-    static bool configured = false;
-    if (!configured) {
-      cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-      if (e != cudaSuccess) return int(e);
-      configured = true;
-    }
-    return pdl_launch(attn_prefill_tc_kernel<64>, grid, block, smem, s, mq, mk, mv, p);
-  }
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-    if (e != cudaSuccess) return int(e);
-    configured = true;
-  }
-  return pdl_launch(attn_prefill_tc_kernel<128>, grid, block, smem, s, mq, mk, mv, p);
+  if (hd == 64) return launch_prefill_tc<64, false>(mq, mk, mv, p, grid, s);
+  if (hd == 128) return launch_prefill_tc<128, false>(mq, mk, mv, p, grid, s);
+  return launch_prefill_tc<256, true>(mq, mk, mv, p, grid, s);
 }
 
 // Reads and clears the error word of the kernel (0 = no bounded wait ever ran out); else

@@ -47,7 +47,7 @@ int kvcm_attention_decode_bf16(const void*, int, void*, int, const void*, const 
 int kvcm_attention_tcgen05_supports(int, int);
 int kvcm_attention_prefill_tcgen05_bf16(const void*, int, int, void*, int, const void*, const void*, int, const int*, int,
                                         const int*, const int*, const int*, const int*, const int*, int, int, int, int, int,
-                                        float, int, float, const float*, void*);
+                                        float, int, int, float, const float*, void*);
 int kvcm_attention_prefill_bf16(const void*, int, void*, int, const void*, const void*, const int*, int, const int*,
                                 const int*, const int*, const int*, const int*, int, int, int, int, int, float, int, float, const float*,
                                 void*);
@@ -185,7 +185,7 @@ int attention(const KvcmForwardArgs& a, const KvcmForwardLayer& L, const void* q
       return kvcm_attention_prefill_tcgen05_bf16(q, q_stride, a.rows, a.attn, a.nh * a.hd, L.k_cache, L.v_cache, L.num_pages,
                                                  tables, a.max_blocks, a.tile_seq, a.tile_q0, a.seq_q_start, a.seq_q_len,
                                                  a.seq_ctx_len, a.prefill_tiles, a.nh, a.nkv, a.hd, a.block_size, a.scale,
-                                                 L.window, 0.f, nullptr, s);
+                                                 L.window, 0, 0.f, nullptr, s);
     return kvcm_attention_prefill_bf16(q, q_stride, a.attn, a.nh * a.hd, L.k_cache, L.v_cache, tables, a.max_blocks,
                                        a.tile_seq, a.tile_q0, a.seq_q_start, a.seq_q_len, a.seq_ctx_len, a.prefill_tiles,
                                        a.nh, a.nkv, a.hd, a.block_size, a.scale, L.window, 0.f, nullptr, s);

@@ -507,7 +507,8 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
                       keep_first: int = 0) -> None:
     """Rows of portions longer than one token; q/out are the step's full row arrays.
     ``ctx.options['attn_prefill']``: 'tcgen05' | 'mma' force a kernel; 'auto' takes the tcgen05
-    kernel where it supports the sizes (head_dim 64 or 128; pages of 8 to 64 keys dividing 64, or multiples of 64)."""
+    kernel where it supports the sizes (head_dim 64 or 128, 256 when keys and values are the same pages; pages of
+    8 to 64 keys dividing 64, or multiples of 64)."""
     _cuda(q, out, k_cache, v_cache, block_tables, sink)
     _need(sink is None or (sink.dtype == torch.float32 and sink.is_contiguous() and sink.numel() == nh),
           "attention_prefill: sink float32 [heads]")
@@ -519,14 +520,15 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
     _need(ctx.tile_rows == 64, "attention_prefill: the batch must be tiled in 64 query rows")
     mode = ctx.options.get("attn_prefill", "auto")
     B = k_cache.shape[2]
-    kept = int(keep_first) if window > 0 else 0          # the tcgen05 kernel walks one run of keys per row tile
-    if kept == 0 and mode != "mma" and (mode == "tcgen05" or prefill_tcgen05_supported(hd, B)):
+    kept = int(keep_first) if window > 0 else 0
+    shared_kv = k_cache.data_ptr() == v_cache.data_ptr()
+    if mode != "mma" and (mode == "tcgen05" or prefill_tcgen05_supported(hd, B, shared_kv)):
         _need(out.data_ptr() % 16 == 0 and out.stride(0) % 8 == 0, "attention_prefill: out rows must be 16-byte aligned")
         rc = _lib().kvcm_attention_prefill_tcgen05_bf16(
             _p(q), q.stride(0), q.shape[0], _p(out), out.stride(0), _p(k_cache), _p(v_cache), k_cache.shape[0],
             _p(block_tables), block_tables.shape[1], _p(ctx.tile_seq), _p(ctx.tile_q0), _p(ctx.seq_q_start),
             _p(ctx.seq_q_len), _p(ctx.seq_ctx_len), ctx.prefill_tiles, nh, nkv, hd, B, ctypes.c_float(scale),
-            int(window), ctypes.c_float(softcap), _p(sink), _stream())
+            int(window), kept, ctypes.c_float(softcap), _p(sink), _stream())
         _check(rc, "attention_prefill_tcgen05", f"(hd={hd}, nh={nh}, nkv={nkv}, block={B})")
         return
     rc = _lib().kvcm_attention_prefill_keep_bf16(
@@ -537,8 +539,9 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
     _check(rc, "attention_prefill", f"(hd={hd}, nh={nh}, nkv={nkv})")
 
 
-def prefill_tcgen05_supported(hd: int, block_size: int) -> bool:
-    return bool(_lib().kvcm_attention_tcgen05_supports(int(hd), int(block_size)))
+def prefill_tcgen05_supported(hd: int, block_size: int, shared_kv: bool = False) -> bool:
+    """``shared_kv``: keys and values are the same pages (attention over a cached latent), which opens head_dim 256."""
+    return bool(_lib().kvcm_attention_tcgen05_supports_kv(int(hd), int(block_size), int(bool(shared_kv))))
 
 
 def attention_tcgen05_error() -> int:

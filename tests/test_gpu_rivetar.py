@@ -420,7 +420,7 @@ def test_kept_first_keys_in_every_attention_kernel():
     """The tensor-core attention kernels (decode in one block, split over a cluster, split through scratch
     memory; prefill) against the plain kernel, with a window, kept first tokens and a sink; contexts in which the
     kept keys share a tile with the window, lie tiles before it, and outnumber a tile."""
-    for window, keep, hd in ((100, 7, 64), (300, 70, 96), (64, 130, 32), (500, 1, 128)):
+    for window, keep, hd in ((100, 7, 64), (300, 70, 96), (64, 130, 32), (500, 1, 128), (200, 130, 64), (129, 64, 128)):
         layer = {"type": "attention", "mixer": RM.attn(8, 2, hd, hd - 16, 0.2, (10000.0, 16), window, keep), "mlp": None}
         import tempfile
         folder = RM.write_model_from({"architecture": "Rivetar", "vocab": 64, "width": 64, "norm": {"eps": 1e-6},
@@ -428,15 +428,37 @@ def test_kept_first_keys_in_every_attention_kernel():
         toks = helpers.random_tokens(900, 64, 8)
         outs = {}
         for options in ({"attention": "plain"}, {"attn_parts": 1}, {"attn_parts": 4}, {"attn_parts": 4, "attn_merge": "kernel"},
-                        {"attn_prefill": "mma"}):
+                        {"attn_prefill": "mma"}, {}):
             r = helpers.Replayer(folder, "bfloat16", 1024, 16, options=options)
             o = [r.step([dict(id="a", tokens=toks[:50], want=[3, 49])]),
-                 r.step([dict(id="a", tokens=toks[50:880], want=[0, 60, 100, 500, 829])])]
+                 r.step([dict(id="a", tokens=toks[50:880], want=list(range(0, 830, 23)) + [829])])]
             o += [r.step([dict(id="a", tokens=[t], want=[0])]) for t in toks[880:]]
             outs[json.dumps(options)] = torch.cat(o)
         base = outs.pop(json.dumps({"attention": "plain"}))
         for name, o in outs.items():
             close(o, base, "bfloat16", f"window {window} keep {keep}: {name}")
+
+
+def test_latent_attention_prefill_kernels_agree():
+    """Attention over a cached latent whose page row has 256 elements (keys and values are the same pages): the
+    default prefill kernel against the plain kernel and the other tensor-core one, in portions cut at odd places,
+    beside a second request."""
+    import tempfile
+    layer = {"type": "latent_attention", "mixer": RM.latent(6, 96, 64, 80, 192, 128, 0.06, (10000.0, 64)), "mlp": None}
+    folder = RM.write_model_from({"architecture": "Rivetar", "vocab": 64, "width": 128, "norm": {"eps": 1e-6},
+                                  "layers": [layer]}, 5, "bfloat16", tempfile.mkdtemp())
+    toks, other = helpers.random_tokens(700, 64, 9), helpers.random_tokens(333, 64, 10)
+    outs = {}
+    for options in ({"attention": "plain"}, {"attn_prefill": "mma"}, {}):
+        r = helpers.Replayer(folder, "bfloat16", 1152, 16, options=options)
+        o = [r.step([dict(id="a", tokens=toks[:131], want=[0, 1, 63, 64, 130])]),
+             r.step([dict(id="a", tokens=toks[131:690], want=list(range(0, 559, 29)) + [558]),
+                     dict(id="b", tokens=other, want=[0, 127, 128, 332])])]
+        o += [r.step([dict(id="a", tokens=[t], want=[0])]) for t in toks[690:]]
+        outs[json.dumps(options)] = torch.cat(o)
+    base = outs.pop(json.dumps({"attention": "plain"}))
+    for name, o in outs.items():
+        close(o, base, "bfloat16", f"latent rows of 256: {name}")
 
 
 def test_blocks_with_and_without_the_fused_norms(folders, oracle):
