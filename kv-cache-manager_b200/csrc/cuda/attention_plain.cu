@@ -1,6 +1,6 @@
 // Plain paged attention: one block per (row, query head), keys walked through the page table in
 // chunks with a running (max, sum, accumulator): softmax and P*V in float whatever the storage
-// type.  Any head_dim up to 512, any number of heads and groups, any page size, optional window.
+// type.  Any head_dim up to 1024, any number of heads and groups, any page size, optional window.
 // With float storage this is the attention of the true 32-bit path; with bfloat16 it is the twin
 // that the fast kernels are checked against.  A row's result depends only on its own position,
 // its keys and the window, never on the batch around it.
@@ -18,7 +18,7 @@ namespace kvcm {
 
 constexpr int kPlainThreads = 128;
 constexpr int kPlainChunk = 512;
-constexpr int kPlainMaxDimsPerThread = 4;     // head_dim <= 4 * 128
+constexpr int kPlainMaxDimsPerThread = 8;     // head_dim <= 8 * 128
 
 template <typename T>
 __global__ void __launch_bounds__(kPlainThreads)
@@ -48,7 +48,9 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
 
   float m = sink ? sink[h] : -INFINITY, l = sink ? 1.f : 0.f;
   const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
-  float acc[kPlainMaxDimsPerThread] = {0.f, 0.f, 0.f, 0.f};
+  float acc[kPlainMaxDimsPerThread];
+#pragma unroll
+  for (int i = 0; i < kPlainMaxDimsPerThread; ++i) acc[i] = 0.f;
 
   for (int c0 = 0; c0 < total; c0 += kPlainChunk) {
     const int n = min(kPlainChunk, total - c0);

@@ -256,11 +256,12 @@ delta_scan_kernel(const ScanArgs A) {
   // Elements from dk on stay zero.
   constexpr int CH = NI >= 8 ? NI / 4 : 1;
   auto place = [](int c) { return CH >= 2 ? (c ^ ((c / CH) & 7)) : c; };
-  __shared__ __align__(16) float qs[2][TT][DKP];
-  __shared__ __align__(16) float ks[2][TT][DKP];
-  __shared__ float vs[2][TT][DR_COLS];
-  __shared__ float bs[2][TT], gs[2][TT];
-  __shared__ __align__(16) float gds[CHD ? 2 : 1][CHD ? TT : 1][CHD ? DKP : 4];
+  constexpr int NST = 2;                                  // tiles of tokens in shared memory or on their way
+  __shared__ __align__(16) float qs[NST][TT][DKP];
+  __shared__ __align__(16) float ks[NST][TT][DKP];
+  __shared__ float vs[NST][TT][DR_COLS];
+  __shared__ float bs[NST][TT], gs[NST][TT];
+  __shared__ __align__(16) float gds[CHD ? NST : 1][CHD ? TT : 1][CHD ? DKP : 4];
   const int s = blockIdx.z, head = blockIdx.y;
   const int slot = seq_state_slot[s];
   const int q0 = seq_q_start[s], n = seq_q_len[s];
@@ -284,7 +285,7 @@ delta_scan_kernel(const ScanArgs A) {
     const int i = r * NI + m;
     acc[m] = (col_ok && i < dk) ? S[size_t(i) * dv] : 0.f;
   }
-  for (int idx = threadIdx.x; idx < 2 * TT * DKP; idx += blockDim.x) {
+  for (int idx = threadIdx.x; idx < NST * TT * DKP; idx += blockDim.x) {
     (&qs[0][0][0])[idx] = 0.f;
     (&ks[0][0][0])[idx] = 0.f;
     if constexpr (CHD) (&gds[0][0][0])[idx] = 1.f;
@@ -353,15 +354,24 @@ delta_scan_kernel(const ScanArgs A) {
     asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     __syncthreads();                                   // this tile has landed; the other buffer has been consumed
     if (t0 + TT < n) stage(buf ^ 1, t0 + TT);
-#pragma unroll(LIN ? 4 : 1)
-    for (int t = 0; t < nt; ++t) {
+    // One token: the state's step and the read-out.  `whole` false leaves the read-out as this lane's partial sum
+    // (the caller adds the lanes of a column), so that the shuffles of several tokens can be in flight together.
+    auto token = [&](int t, bool whole) -> float {
       const float g = CHD ? 1.f : gs[buf][t], beta = bs[buf][t];
       float kt[NI], qt[NI];
       if constexpr (CHD) {                            // the rows of S decay each by its own factor first
+        if constexpr (NI % 4 == 0) {
 #pragma unroll
-        for (int m = 0; m < NI; ++m) {
-          const int i = r * NI + m;
-          acc[m] *= gds[buf][t][4 * place(i / 4) + i % 4];
+          for (int m = 0; m < NI; m += 4) {
+            const float4 d = *reinterpret_cast<const float4*>(&gds[buf][t][4 * place((r * NI + m) / 4)]);
+            acc[m] *= d.x; acc[m + 1] *= d.y; acc[m + 2] *= d.z; acc[m + 3] *= d.w;
+          }
+        } else {
+#pragma unroll
+          for (int m = 0; m < NI; ++m) {
+            const int i = r * NI + m;
+            acc[m] *= gds[buf][t][4 * place(i / 4) + i % 4];
+          }
         }
       }
       if constexpr (NI % 4 == 0) {
@@ -425,9 +435,35 @@ delta_scan_kernel(const ScanArgs A) {
           o4[m & 3] = fmaf(acc[m], qt[m], o4[m & 3]);
         }
         o = (o4[0] + o4[1]) + (o4[2] + o4[3]);
+        if (whole) {
 #pragma unroll
-        for (int w = CPW; w < 32; w <<= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
+          for (int w = CPW; w < 32; w <<= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
+        }
       }
+      return o;
+    };
+    int t = 0;
+    if constexpr (LIN && !EARLY) {
+      // The linear forms' step does not wait for the read-out: four tokens' read-outs are reduced side by side
+      // (the same sums in the same order as one by one).
+      for (; t + 4 <= nt; t += 4) {
+        float o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[j] = token(t + j, false);
+#pragma unroll
+        for (int w = CPW; w < 32; w <<= 1) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) o[j] += __shfl_xor_sync(0xffffffffu, o[j], w);
+        }
+        if (r == 0 && col_ok) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) out[size_t(q0 + t0 + t + j) * heads * dv + size_t(head) * dv + col] = o[j];
+        }
+      }
+    }
+#pragma unroll 1
+    for (; t < nt; ++t) {
+      const float o = token(t, true);
       if (r == 0 && col_ok) out[size_t(q0 + t0 + t) * heads * dv + size_t(head) * dv + col] = o;
     }
   }
@@ -530,7 +566,9 @@ static int launch_scan(const ScanArgs& A, int rows, int seqs, cudaStream_t s) {
   }
   // 32 columns a block; 16 or 8 when that leaves SMs without a block (one request's long portion)
   const long long per32 = (long long)seqs * heads * ((dv + 31) / 32);
-  const int cols = per32 >= sms ? 32 : (2 * per32 >= sms ? 16 : 8);
+  // (the linear form with channel-wise decays is bound by its reads of shared memory, which narrower blocks
+  // repeat: 16 columns at least)
+  const int cols = per32 >= sms ? 32 : ((2 * per32 >= sms || MODE == kScanLinearChannel) ? 16 : 8);
   // few warps for the device (one request's long portion with few heads): the form with the shorter chain
   // (it has no meaning for the linear recurrence, whose step does not read the state)
   constexpr bool LIN = MODE == kScanLinear || MODE == kScanLinearChannel;

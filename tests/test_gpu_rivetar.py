@@ -183,6 +183,8 @@ ALONE = [
     ("gla", {"type": "gla", "mixer": RM.gla(4, 6, 10, 4.0, 7), "mlp": None}, {}),
     ("gla_slow_decay_ff", {"type": "gla", "mixer": RM.gla(3, 36, 8, 64.0, 2), "mlp": RM.dense(16)}, {}),
     ("latent", {"type": "latent_attention", "mixer": RM.latent(3, 8, 12, 14, 20, 9, 0.4, (50.0, 8)), "mlp": None}, {}),
+    ("latent_long_rows", {"type": "latent_attention", "mixer": RM.latent(2, 24, 16, 20, 560, 40, 0.05, (50.0, 16)), "mlp": None}, {}),
+    ("gla_long_keys", {"type": "gla", "mixer": RM.gla(2, 200, 24, 8.0, 4), "mlp": None}, {}),
     ("latent_ff_looped", {"type": "latent_attention", "mixer": RM.latent(2, 10, 2, 6, 30, 12, 0.3, (3.0, 2)),
                           "mlp": RM.dense(33)}, {"loop": {"start": 0, "stop": 1, "times": 3}, "logit_softcap": 11.0}),
 ]
@@ -190,8 +192,9 @@ ALONE = [
 
 @pytest.mark.parametrize("layer,top", [(l, t) for _, l, t in ALONE], ids=[n for n, _, _ in ALONE])
 def test_one_layer_alone(tmp_path, layer, top):
-    """One layer of each kind (and the feed-forward with it or without; once as a loop of three passes) in
-    float32: whole, and in portions with single tokens at the end."""
+    """One layer of each kind (and the feed-forward with it or without; once as a loop of three passes; once with a
+    cached latent row and once with keys longer than any tensor-core kernel takes) in float32: whole, and in
+    portions with single tokens at the end."""
     folder = one_layer_model(tmp_path, layer, **top)
     cfg, w = RM.read_model(folder)
     toks = helpers.random_tokens(90, 120, 77)
