@@ -61,11 +61,30 @@ def _bifatar_mini():
             ]}
 
 
+def _rivetar_mini():
+    """A small Rivetar: attention over a cached latent with a rotated key part, a looped span of gated linear
+    attention and windowed attention that keeps the first tokens, a latent layer behind the loop."""
+    dense = {"kind": "dense", "ff": 640}
+    latent = {"heads": 6, "dim": 48, "rot_dim": 32, "vdim": 64, "kv_rank": 96, "q_rank": 160, "scale": 0.11,
+              "rot": {"base": 100000.0, "dims": 32}}
+    return {"architecture": "Rivetar", "vocab": 1000, "width": 384, "norm": {"eps": 1e-5}, "embedding": {"scale": 2.0},
+            "logit_softcap": 25.0, "loop": {"start": 1, "stop": 3, "times": 2},
+            "layers": [
+                {"type": "latent_attention", "mixer": latent, "mlp": dense},
+                {"type": "gla", "mixer": {"heads": 6, "dim": 32, "vdim": 64, "tau": 8.0, "decay_rank": 24}, "mlp": None},
+                {"type": "attention", "mixer": {"heads": 6, "kv_heads": 2, "dim": 64, "vdim": 32, "scale": 0.125,
+                                                "rot": {"base": 10000.0, "dims": 32}, "mask": {"size": 90, "keep_first": 3}},
+                 "mlp": dense},
+                {"type": "latent_attention", "mixer": latent, "mlp": dense},
+            ]}
+
+
 PRESETS = {
     # name: (config.json keys, seed, norm jitter); keys with "architecture" go through the registry,
     # the others are those of a Llama dense decoder
     "tolanex-mini": (_tolanex_mini(), 4, 0.1),
     "bifatar-mini": (_bifatar_mini(), 5, 0.1),
+    "rivetar-mini": (_rivetar_mini(), 7, 0.1),
     "tiny-a": (dict(vocab_size=256, hidden_size=64, intermediate_size=172, num_hidden_layers=2,
                     num_attention_heads=4, num_key_value_heads=2, head_dim=16, max_position_embeddings=128,
                     rope_theta=10000.0, rms_norm_eps=1e-5, tie_word_embeddings=False), 0, 0.0),

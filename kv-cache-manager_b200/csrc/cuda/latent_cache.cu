@@ -44,18 +44,19 @@ latent_rope_cache_kernel(const float* __restrict__ proj, int ldp, const float* _
   pdl_wait();
   const int row = blockIdx.x;
   const float* src = proj + size_t(row) * ldp;
+  // Both norms' sums are taken before the first barrier, so that all loads of the row are in flight together.
+  const int slot = slot_mapping[row];
+  const float* c = src + qr;
+  float ssq = 0.f, ss = 0.f;
+  for (int i = threadIdx.x; i < qr; i += blockDim.x) ssq = fmaf(src[i], src[i], ssq);
+  if (slot >= 0)
+    for (int i = threadIdx.x; i < R; i += blockDim.x) ss = fmaf(c[i], c[i], ss);
   if (qr > 0) {
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < qr; i += blockDim.x) ss = fmaf(src[i], src[i], ss);
-    ss = block_sum(ss, scratch);
-    const float inv = 1.f / sqrtf(ss / float(qr) + eps);
+    ssq = block_sum(ssq, scratch);
+    const float inv = 1.f / sqrtf(ssq / float(qr) + eps);
     for (int i = threadIdx.x; i < qr; i += blockDim.x) stf(cq_out + size_t(row) * qr + i, wq[i] * (src[i] * inv));
   }
-  const int slot = slot_mapping[row];
   if (slot < 0) return;                                   // a padding row holds no page
-  const float* c = src + qr;
-  float ss = 0.f;
-  for (int i = threadIdx.x; i < R; i += blockDim.x) ss = fmaf(c[i], c[i], ss);
   ss = block_sum(ss, scratch);
   const float inv = 1.f / sqrtf(ss / float(R) + eps);
   T* dst = cache + size_t(slot) * HD;

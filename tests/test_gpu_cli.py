@@ -93,3 +93,16 @@ def test_kvbench_and_kvcorrect_on_the_bifatar_preset():
     assert rc in (0, 2), out[-2000:] + err[-2000:]
     assert "[PASS] alone (scattered pages) = batch" in out and "[PASS] paged = contiguous" in out
     assert "[SKIP] prefix cache" in out
+
+
+def test_kvbench_and_kvcorrect_on_the_rivetar_preset():
+    """A fourth architecture through the same flags: a looped span whose passes have pages and state of their own,
+    a window that keeps a request's first pages, a latent cache, served by the scheduler, and kvcorrect's checks."""
+    rc, out, err = run("kvbench", "--preset", "rivetar-mini", "--requests", "10", "--rate", "0", "--prompt-len", "60",
+                       "--output-len", "12", "--max-seq-len", "128", "--num-blocks", "48", "--max-num-seqs", "4",
+                       "--max-batched-tokens", "96", "--warmup", "1")
+    assert rc == 0, err[-2000:]
+    assert "completed 10/10" in out
+    rc, out, err = run("kvcorrect", "--preset", "rivetar-mini", "--steps", "8", "--prompts", "3", "--prompt-len", "40")
+    assert rc in (0, 2), out[-2000:] + err[-2000:]
+    assert "[PASS] alone (scattered pages) = batch" in out and "[PASS] paged = contiguous" in out
