@@ -93,3 +93,72 @@ def test_random_configuration(seed, tmp_path):
         assert at == 75
         check(torch.cat(outs), ref, f"seed {seed} in portions")
         check(torch.cat(second), ref2[:at2], f"seed {seed} second request")
+
+
+def draw_larger(seed: int) -> dict:
+    """Sizes of a small real model: widths of 128 to 512, heads of 32 to 128, cached latent rows of 72 to 384
+    elements (beyond 256 the plain attention kernel serves them), three to eight layers."""
+    r = random.Random(1000 + seed)
+    layers = []
+    for i in range(r.randint(3, 8)):
+        kind = r.choice(["attention", "latent_attention", "latent_attention", "gla"])
+        if kind == "attention":
+            kv, dim = r.choice([1, 2, 4]), r.choice([32, 48, 64, 96, 128])
+            m = RM.attn(kv * r.choice([1, 2, 4]), kv, dim, r.choice([32, 48, 64, 96, 128]), round(dim ** -0.5, 4),
+                        (r.choice([10000.0, 20000.0, 500000.0]), r.choice([d for d in (16, 32, 48, 64, 96, 128) if d <= dim])))
+            if r.random() < 0.9:
+                m["mask"] = {"size": r.choice([16, 24, 50, 64, 72, 100, 128, 200]), "keep_first": r.choice([0, 1, 2, 4, 8])}
+        elif kind == "latent_attention":
+            rot, dim = r.choice([8, 16, 32, 64]), r.choice([32, 64, 96, 128])
+            m = RM.latent(r.choice([2, 4, 6, 8]), dim, rot, r.choice([32, 48, 64, 128]), r.choice([64, 96, 128, 192, 256, 320]),
+                          r.choice([64, 128, 192, 256]), round((dim + rot) ** -0.5, 4), (r.choice([10000.0, 250000.0]), rot))
+        else:
+            m = RM.gla(r.choice([1, 2, 4]), r.choice([32, 48, 64, 128]), r.choice([32, 64, 96]), r.choice([4.0, 16.0, 32.0]),
+                       r.choice([8, 16, 32]))
+        layers.append({"type": kind, "mixer": m, "mlp": RM.dense(r.choice([256, 512, 768, 1024])) if r.random() < 0.8 else None})
+    cfg = {"architecture": "Rivetar", "vocab": r.choice([512, 1000, 2048]), "width": r.choice([128, 192, 320, 384, 512]),
+           "norm": {"eps": r.choice([1e-6, 1e-5])}, "embedding": {"scale": r.choice([1.0, 2.0, 8.0])}, "layers": layers,
+           "logit_softcap": r.choice([20.0, 50.0])}
+    if r.random() < 0.85:
+        a = r.randrange(len(layers))
+        cfg["loop"] = {"start": a, "stop": r.randint(a + 1, len(layers)), "times": r.choice([1, 2, 2, 3])}
+    return cfg
+
+
+def spread_error(got, ref):
+    d = got.double().cpu() - ref.double().cpu()
+    d = d - d.mean(dim=-1, keepdim=True)
+    return d.pow(2).mean(dim=-1).sqrt() / ref.double().std().item()
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_configuration_at_larger_sizes(seed, tmp_path):
+    """Pages of 64, a prompt of 330 tokens whole and in portions cut at random beside a second request, float32:
+    every position within 2e-4 of the logits' spread; bfloat16: the typical position within 3 %."""
+    cfg = draw_larger(seed)
+    n = 330
+    toks, other = helpers.random_tokens(n, cfg["vocab"], 40 + seed), helpers.random_tokens(200, cfg["vocab"], 80 + seed)
+    for dtype in ("float32", "bfloat16"):
+        folder = RM.write_model_from(cfg, 300 + seed, dtype, str(tmp_path / dtype))
+        cfg_read, w = RM.read_model(folder)
+        ref, ref2 = P.forward(cfg_read, w, toks), P.forward(cfg_read, w, other)
+        r = helpers.Replayer(folder, dtype, 768, 64, max_live=4)
+        errs = [spread_error(r.step([dict(id="w", tokens=toks, want=list(range(n)))], end=["w"]), ref)]
+        rnd, at, at2, outs, second = random.Random(seed), 0, 0, [], []
+        while at < n:
+            k = min(rnd.choice([1, 2, 3, 40, 64, 65, 100]) if at < 250 else 1, n - at)
+            entries = [dict(id="p", tokens=toks[at:at + k], want=list(range(k)))]
+            k2 = min(rnd.choice([1, 2, 17]), len(other) - at2)
+            if k2 > 0:
+                entries.append(dict(id="q", tokens=other[at2:at2 + k2], want=list(range(k2))))
+            out = r.step(entries)
+            outs.append(out[:k])
+            second.append(out[k:])
+            at, at2 = at + k, at2 + max(k2, 0)
+        errs += [spread_error(torch.cat(outs), ref), spread_error(torch.cat(second), ref2[:at2])]
+        for what, e in zip(("whole", "in portions", "second request"), errs):
+            assert torch.isfinite(e).all(), f"seed {seed} {dtype} {what}: non-finite ({cfg})"
+            if dtype == "float32":
+                assert e.max().item() < 2e-4, f"seed {seed} float32 {what}: {e.max().item():.2e} at {int(e.argmax())} ({cfg})"
+            else:
+                assert e.median().item() < 0.03, f"seed {seed} bfloat16 {what}: median {e.median().item():.3f} ({cfg})"
