@@ -298,12 +298,16 @@ delta_scan_kernel(const ScanArgs A) {
   const bool vec16 = (dk % 4) == 0 && (channels % 4) == 0 && (A.q_base % 4) == 0 && (A.k_base % 4) == 0 &&
                      (reinterpret_cast<uintptr_t>(qkv) & 15) == 0;
 
+  // The 16-byte pieces of a tile are dealt out to the threads in the order (token, piece); a thread's first piece
+  // and its step from one piece to its next are the same in every tile, so no loop below divides.
+  const int per = max(dk / 4, 1);
+  const int st_t0 = threadIdx.x / per, st_c0 = threadIdx.x % per, st_dt = blockDim.x / per, st_dc = blockDim.x % per;
+  float* __restrict__ out_col = out + size_t(q0) * heads * dv + size_t(head) * dv + col;   // this column's outputs
+  const size_t out_ld = size_t(heads) * dv;
   auto stage = [&](int buf, int t0) {                   // asks for the tile of tokens t0 .. t0 + TT - 1
     const int nt = min(TT, n - t0);
     if (vec16) {
-      const int per = dk / 4;
-      for (int idx = threadIdx.x; idx < TT * per; idx += blockDim.x) {
-        const int t = idx / per, c = idx % per;
+      for (int t = st_t0, c = st_c0; t < TT; t += st_dt + (c + st_dc >= per), c = c + st_dc >= per ? c + st_dc - per : c + st_dc) {
         const bool ok = t < nt;
         const float* src = qkv + (ok ? size_t(q0 + t0 + t) * channels + 4 * c : 0);
         dr_copy16(&qs[buf][t][4 * place(c)], src + (ok ? q_off : 0), ok);
@@ -331,9 +335,7 @@ delta_scan_kernel(const ScanArgs A) {
     }
     if constexpr (CHD) {
       if (gvec16) {
-        const int per = dk / 4;
-        for (int idx = threadIdx.x; idx < TT * per; idx += blockDim.x) {
-          const int t = idx / per, c = idx % per;
+        for (int t = st_t0, c = st_c0; t < TT; t += st_dt + (c + st_dc >= per), c = c + st_dc >= per ? c + st_dc - per : c + st_dc) {
           const bool ok = t < nt;
           dr_copy16(&gds[buf][t][4 * place(c)], A.gd + (ok ? size_t(q0 + t0 + t) * gd_ld + gd_off + 4 * c : 0), ok);
         }
@@ -457,14 +459,14 @@ delta_scan_kernel(const ScanArgs A) {
         }
         if (r == 0 && col_ok) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) out[size_t(q0 + t0 + t + j) * heads * dv + size_t(head) * dv + col] = o[j];
+          for (int j = 0; j < 4; ++j) out_col[size_t(t0 + t + j) * out_ld] = o[j];
         }
       }
     }
 #pragma unroll 1
     for (; t < nt; ++t) {
       const float o = token(t, true);
-      if (r == 0 && col_ok) out[size_t(q0 + t0 + t) * heads * dv + size_t(head) * dv + col] = o;
+      if (r == 0 && col_ok) out_col[size_t(t0 + t) * out_ld] = o;
     }
   }
 #pragma unroll
