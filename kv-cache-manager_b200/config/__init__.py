@@ -1,12 +1,12 @@
 """Configuration: typed model configs, the architecture registry, engine-side settings."""
-from .model_config import (BifatarConfig, ConfigError, LlamaConfig, ModelConfig, RivetarConfig, TolanexConfig,
+from .model_config import (BifatarConfig, ConfigError, LlamaConfig, LobutarConfig, ModelConfig, RivetarConfig, TolanexConfig,
                            read_config_json)
 from .registry import (ArchitectureEntry, config_from_dict, get_architecture, load_config,
                        register_architecture, registered_architectures)
 from .engine_config import (EngineConfig, KVManagerConfig, SchedulerConfig, canonical_dtype)
 
 __all__ = [
-    "BifatarConfig", "ConfigError", "LlamaConfig", "ModelConfig", "RivetarConfig", "TolanexConfig", "read_config_json", "ArchitectureEntry",
+    "BifatarConfig", "ConfigError", "LlamaConfig", "LobutarConfig", "ModelConfig", "RivetarConfig", "TolanexConfig", "read_config_json", "ArchitectureEntry",
     "config_from_dict", "get_architecture", "load_config", "register_architecture",
     "registered_architectures", "EngineConfig", "KVManagerConfig", "SchedulerConfig",
     "canonical_dtype",

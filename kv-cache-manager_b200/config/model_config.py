@@ -507,3 +507,105 @@ class RivetarConfig(ModelConfig):
         if self.has_loop:
             d["loop"] = {"start": self.loop_start, "stop": self.loop_stop, "times": self.loop_times}
         return d
+
+
+# ------------------------------------------------------------------------------------ Lobutar
+
+@dataclass(frozen=True)
+class LobutarConfig(ModelConfig):
+    """Lobutar: a decoder whose layers are listed one by one, pre-norm layers over ``streams`` residual streams
+    (hyper-connections), a layer optionally running with an earlier layer's weights.
+
+    Top level: ``vocab``, ``width``, ``norm.eps``, ``streams`` and ``layers``: a list of {type, mixer, mlp, weights_of}.
+    ``type`` "attention" (differential attention): mixer {heads, kv_heads, dim, vdim, diff, scale, rot {base, dims}};
+    "latent_attention": mixer {heads, dim, rot_dim, vdim, kv_rank, scale, rot {base, dims}, mask {size} (optional)}.
+    ``mlp`` is null, {kind: "dense", ff} or {kind: "moe", expert {ff}, router {experts, top, scale, groups {count, keep}},
+    shared {ff} (optional)}.  ``weights_of``: j (optional): the layer has no tensors of its own and runs with layer j's
+    (its entry otherwise equals layer j's).  ``layers`` is kept as the parsed JSON after validation; the builder reads
+    every size from it."""
+    vocab: int = 0
+    width: int = 0
+    norm_eps: float = 1e-6
+    streams: int = 1
+    layers: tuple = ()
+
+    @classmethod
+    def from_json_dict(cls, d: Dict[str, Any]) -> "LobutarConfig":
+        w = "config.json (Lobutar)"
+        norm = _section(d, "norm", w)
+        layers = d.get("layers")
+        if not isinstance(layers, list) or not layers:
+            raise ConfigError(f"{w}: 'layers' must be a non-empty list")
+        cfg = cls(architecture="Lobutar", vocab=_require(d, "vocab", int, w), width=_require(d, "width", int, w),
+                  norm_eps=_require(norm, "eps", float, w + " norm"), streams=_require(d, "streams", int, w),
+                  layers=tuple(json.loads(json.dumps(layers))))
+        cfg.validate()
+        return cfg
+
+    def validate(self) -> None:
+        w = "LobutarConfig"
+        if self.vocab <= 0 or self.width <= 0:
+            raise ConfigError(f"{w}: 'vocab' and 'width' must be positive")
+        if not (self.norm_eps > 0):
+            raise ConfigError(f"{w}: norm.eps must be positive, got {self.norm_eps}")
+        if not (1 <= self.streams <= 16):
+            raise ConfigError(f"{w}: 'streams' must lie in 1..16, got {self.streams}")
+        for i, layer in enumerate(self.layers):
+            lw = f"{w}: layer {i}"
+            if not isinstance(layer, dict):
+                raise ConfigError(f"{lw} must be an object")
+            src = layer.get("weights_of")
+            if src is not None:
+                if isinstance(src, bool) or not isinstance(src, int) or not (0 <= src < i) or self.layers[src].get("weights_of") is not None:
+                    raise ConfigError(f"{lw}: weights_of must name an earlier layer that has tensors of its own, got {src!r}")
+                ref = self.layers[src]
+                if any(layer.get(k) != ref.get(k) for k in ("type", "mixer", "mlp")):
+                    raise ConfigError(f"{lw}: a layer that runs with layer {src}'s weights must have the same type, mixer and mlp")
+            kind = layer.get("type")
+            m = _section(layer, "mixer", lw)
+            mw = lw + " mixer"
+            if kind == "attention":
+                _check_heads(m, mw)
+                _require(m, "scale", float, mw)
+                _require(m, "diff", float, mw)
+                _check_rot(m, mw)
+            elif kind == "latent_attention":
+                _positive_ints(m, ("heads", "dim", "rot_dim", "vdim", "kv_rank"), mw)
+                _require(m, "scale", float, mw)
+                rot = _section(m, "rot", mw)
+                dims = _require(rot, "dims", int, mw + " rot")
+                if _require(rot, "base", float, mw + " rot") <= 0 or dims <= 0 or dims % 2 or dims > m["rot_dim"]:
+                    raise ConfigError(f"{mw}: rot needs a positive base and an even 'dims' within 'rot_dim', got {rot!r}")
+                mask = _section(m, "mask", mw, optional=True)
+                if mask is not None and _require(mask, "size", int, mw + " mask") <= 0:
+                    raise ConfigError(f"{mw}: mask.size must be positive")
+            else:
+                raise ConfigError(f"{lw}: unknown type {kind!r} (known: attention, latent_attention)")
+            mlp = layer.get("mlp")
+            if mlp is None:
+                continue
+            pw = lw + " mlp"
+            if not isinstance(mlp, dict) or mlp.get("kind") not in ("dense", "moe"):
+                raise ConfigError(f"{lw}: mlp must be null or of kind 'dense' or 'moe', got {mlp!r}")
+            if mlp["kind"] == "dense":
+                _positive_ints(mlp, ("ff",), pw)
+                continue
+            _positive_ints(_section(mlp, "expert", pw), ("ff",), pw + " expert")
+            r = _section(mlp, "router", pw)
+            _positive_ints(r, ("experts", "top"), pw + " router")
+            if "scale" in r:
+                _require(r, "scale", float, pw + " router")
+            g = _section(r, "groups", pw + " router", optional=True)
+            count, keep = 1, 1
+            if g is not None:
+                _positive_ints(g, ("count", "keep"), pw + " router groups")
+                count, keep = g["count"], g["keep"]
+            if r["experts"] % count or keep > count or r["top"] > (r["experts"] // count) * keep:
+                raise ConfigError(f"{pw}: {r['experts']} experts in {count} groups of which {keep} are kept cannot give {r['top']} choices")
+            shared = _section(mlp, "shared", pw, optional=True)
+            if shared is not None:
+                _positive_ints(shared, ("ff",), pw + " shared")
+
+    def to_json_dict(self) -> Dict[str, Any]:
+        return {"architecture": self.architecture, "vocab": self.vocab, "width": self.width, "norm": {"eps": self.norm_eps},
+                "streams": self.streams, "layers": json.loads(json.dumps(list(self.layers)))}

@@ -18,6 +18,13 @@
 //        [pages, nkv, page, HD]; HD >= max(dk, dv), elements beyond a head's own size are zero
 //        (zeros add nothing to a score, and the attention output's columns beyond dv stay zero).
 //
+// With `maps` = M > 1 every query head and every key head holds M score maps side by side (the projection's
+// q is nh*M*dk wide, head by head [map 0 | map 1 | ..], k is nkv*M*dk): bias, rotation and per-head norm work on
+// each map's dk elements; q_out gets nh*M heads of HD, head h*M+m holding map m of query head h at elements
+// [m*dk, (m+1)*dk) and zeros elsewhere; the key slot of head g holds its M maps one after another.  A query head
+// of q_out therefore meets only its own map of the cached key, and the nh*M heads share the nkv key/value heads
+// in the usual grouped way (M*dk <= HD).
+//
 // All arithmetic is float; the order of steps is the parameter list's, so a mixer that wants the
 // norm before the rotation uses step 2 and one that wants it after uses step 4.
 #include "common.cuh"
@@ -38,6 +45,7 @@ struct AttnPrepareParams {
   int nh, nkv, dk, dv, HD;
   int interleaved;                   // pairs (2i, 2i+1) instead of (i, i + half)
   const float* v_inv_freq;           // [dv/2] or null
+  int maps;                          // score maps per head (1: ordinary attention)
 };
 
 __device__ __forceinline__ void store_pair(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
@@ -53,7 +61,8 @@ attn_prepare_kernel(AttnPrepareParams p) {
   pdl_launch_dependents();
   const int r = blockIdx.x, tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
-  const int nq = p.nh * p.dk, nk = p.nkv * p.dk, nv = p.nkv * p.dv;
+  const int M = p.maps, nqu = p.nh * M, nku = p.nkv * M;         // units of dk elements: a map of a q or k head
+  const int nq = nqu * p.dk, nk = nku * p.dk, nv = p.nkv * p.dv;
   const int n = nq + nk + nv;
   const int half = p.rot / 2;
   float* cs_table = row + n;
@@ -94,13 +103,13 @@ attn_prepare_kernel(AttnPrepareParams p) {
   const size_t base = (size_t(page) * p.nkv * p.block_size + off) * p.HD;
   const size_t head_stride = size_t(p.block_size) * p.HD;
   const float lam = p.v_first ? p.lambda[0] : 0.f;
-  for (int u = warp; u < p.nh + 2 * p.nkv; u += nwarps) {
-    if (u < p.nh + p.nkv) {                          // a query or key head
-      const bool is_q = u < p.nh;
+  for (int u = warp; u < nqu + nku + p.nkv; u += nwarps) {
+    if (u < nqu + nku) {                             // a query or key head (one map of it)
+      const bool is_q = u < nqu;
       float* x = row + size_t(u) * p.dk;             // q heads, then k heads: both dk wide and adjacent
       if (p.wq) {
         const float inv = is_q ? iq : ik;
-        const float* w = is_q ? p.wq + size_t(u) * p.dk : p.wk + size_t(u - p.nh) * p.dk;
+        const float* w = is_q ? p.wq + size_t(u) * p.dk : p.wk + size_t(u - nqu) * p.dk;
         for (int i = lane; i < p.dk; i += 32) x[i] = x[i] * inv * w[i];
         __syncwarp();
       }
@@ -120,13 +129,24 @@ attn_prepare_kernel(AttnPrepareParams p) {
         inv = 1.f / sqrtf(ss / float(p.dk) + p.eps);
       }
       T* dst;
-      if (is_q) dst = reinterpret_cast<T*>(p.q_out) + (size_t(r) * p.nh + u) * p.HD;
-      else if (slot >= 0) dst = reinterpret_cast<T*>(p.k_cache) + base + (u - p.nh) * head_stride;
+      if (is_q) dst = reinterpret_cast<T*>(p.q_out) + (size_t(r) * nqu + u) * p.HD;
+      else if (slot >= 0) dst = reinterpret_cast<T*>(p.k_cache) + base + ((u - nqu) / M) * head_stride;
       else continue;
-      for (int d = 2 * lane; d < p.HD; d += 64)
-        store_pair(dst + d, d < p.dk ? x[d] * inv : 0.f, d + 1 < p.dk ? x[d + 1] * inv : 0.f);
+      if (M == 1) {
+        for (int d = 2 * lane; d < p.HD; d += 64)
+          store_pair(dst + d, d < p.dk ? x[d] * inv : 0.f, d + 1 < p.dk ? x[d + 1] * inv : 0.f);
+      } else {
+        const int m = (is_q ? u : u - nqu) % M, lo = m * p.dk;
+        if (is_q) {                                  // the whole padded head: the map at its place, zeros around it
+          for (int d = lane; d < p.HD; d += 32) stf(dst + d, d >= lo && d < lo + p.dk ? x[d - lo] * inv : 0.f);
+        } else {                                     // this map's part of the key; the last map also the zeros behind
+          for (int d = lane; d < p.dk; d += 32) stf(dst + lo + d, x[d] * inv);
+          if (m == M - 1)
+            for (int d = M * p.dk + lane; d < p.HD; d += 32) stf(dst + d, 0.f);
+        }
+      }
     } else {                                         // a value head
-      const int head = u - p.nh - p.nkv;
+      const int head = u - nqu - nku;
       float* x = row + nq + nk + size_t(head) * p.dv;
       const size_t at = size_t(r) * nv + size_t(head) * p.dv;
       if (p.v_keep || p.v_first) {
@@ -157,15 +177,17 @@ attn_prepare_kernel(AttnPrepareParams p) {
 template <typename T>
 int launch_attn_prepare(const AttnPrepareParams& p, int rows, cudaStream_t s) {
   if (rows == 0) return 0;
-  if (p.rot % 2 || p.rot > p.dk || p.HD < p.dk || p.HD < p.dv || p.HD % 2 || (p.v_inv_freq && p.dv % 2)) return KVCM_ERR_UNSUPPORTED;
-  const size_t smem = size_t(p.nh * p.dk + p.nkv * p.dk + p.nkv * p.dv + p.rot + (p.v_inv_freq ? p.dv : 0)) * sizeof(float);
+  if (p.rot % 2 || p.rot > p.dk || p.maps < 1 || p.HD < p.maps * p.dk || p.HD < p.dv || p.HD % 2 || (p.v_inv_freq && p.dv % 2) ||
+      (p.maps > 1 && p.wq))
+    return KVCM_ERR_UNSUPPORTED;
+  const size_t smem = size_t((p.nh + p.nkv) * p.maps * p.dk + p.nkv * p.dv + p.rot + (p.v_inv_freq ? p.dv : 0)) * sizeof(float);
   if (smem > 200 * 1024) return KVCM_ERR_UNSUPPORTED;
   if (smem > 48 * 1024) {
     const cudaError_t e = cudaFuncSetAttribute(attn_prepare_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     if (e != cudaSuccess) return int(e);
   }
   // a row of a few thousand elements is a chain of short passes: more threads, fewer turns each
-  const int threads = (p.nh + 2 * p.nkv) * p.HD >= 2048 ? 512 : 256;
+  const int threads = (p.nh * p.maps + 2 * p.nkv) * p.HD >= 2048 ? 512 : 256;
   return pdl_launch(attn_prepare_kernel<T>, dim3(rows), dim3(threads), smem, s, p);
 }
 
@@ -177,7 +199,7 @@ using namespace kvcm;
   const float *proj, int ldp, const float *bias, const float *wq, const float *wk, const int *positions,              \
       const float *inv_freq, int rot, int head_norm, float eps, float *v_keep, const float *v_first,                  \
       const float *lambda, const int *slot_mapping, int block_size, void *q_out, void *k_cache, void *v_cache,        \
-      int rows, int nh, int nkv, int dk, int dv, int HD, int interleaved, const float *v_inv_freq, void *stream
+      int rows, int nh, int nkv, int dk, int dv, int HD, int interleaved, const float *v_inv_freq, int maps, void *stream
 
 static AttnPrepareParams make_params(KVCM_ATTN_PREPARE_ARGS) {
   (void)rows; (void)stream;
@@ -185,17 +207,17 @@ static AttnPrepareParams make_params(KVCM_ATTN_PREPARE_ARGS) {
   p.proj = proj; p.ldp = ldp; p.bias = bias; p.wq = wq; p.wk = wk; p.positions = positions; p.inv_freq = inv_freq;
   p.rot = inv_freq ? rot : 0; p.head_norm = head_norm; p.eps = eps; p.v_keep = v_keep; p.v_first = v_first; p.lambda = lambda;
   p.slot_mapping = slot_mapping; p.block_size = block_size; p.q_out = q_out; p.k_cache = k_cache; p.v_cache = v_cache;
-  p.nh = nh; p.nkv = nkv; p.dk = dk; p.dv = dv; p.HD = HD; p.interleaved = interleaved; p.v_inv_freq = v_inv_freq;
+  p.nh = nh; p.nkv = nkv; p.dk = dk; p.dv = dv; p.HD = HD; p.interleaved = interleaved; p.v_inv_freq = v_inv_freq; p.maps = maps;
   return p;
 }
 
 KVCM_API int kvcm_attn_prepare_f32(KVCM_ATTN_PREPARE_ARGS) {
   return launch_attn_prepare<float>(make_params(proj, ldp, bias, wq, wk, positions, inv_freq, rot, head_norm, eps, v_keep,
                                                 v_first, lambda, slot_mapping, block_size, q_out, k_cache, v_cache, rows, nh,
-                                                nkv, dk, dv, HD, interleaved, v_inv_freq, stream), rows, (cudaStream_t)stream);
+                                                nkv, dk, dv, HD, interleaved, v_inv_freq, maps, stream), rows, (cudaStream_t)stream);
 }
 KVCM_API int kvcm_attn_prepare_bf16(KVCM_ATTN_PREPARE_ARGS) {
   return launch_attn_prepare<bf16>(make_params(proj, ldp, bias, wq, wk, positions, inv_freq, rot, head_norm, eps, v_keep,
                                                v_first, lambda, slot_mapping, block_size, q_out, k_cache, v_cache, rows, nh,
-                                               nkv, dk, dv, HD, interleaved, v_inv_freq, stream), rows, (cudaStream_t)stream);
+                                               nkv, dk, dv, HD, interleaved, v_inv_freq, maps, stream), rows, (cudaStream_t)stream);
 }

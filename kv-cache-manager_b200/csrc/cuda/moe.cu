@@ -4,7 +4,10 @@
 //            experts of the best `keep` of `groups` equal groups of neighbours may be chosen (a
 //            group's score is its largest expert score), the `top` largest scores win; a row's
 //            weights are its chosen scores times `scale`, not renormalised.  An extra row of the
-//            router matrix, if present, is a per-row gate: sigmoid of its logit.
+//            router matrix, if present, is a per-row gate: sigmoid of its logit.  Options: scores
+//            sigmoid(z) instead of the softmax; a `correction` per expert that is added to the scores
+//            for the choice only (choice scores may then be negative; the weights use the scores
+//            themselves); a group's score as the sum of its two largest choice scores.
 //   sort     the (row, choice) pairs ordered by expert, cut into tiles of 64 pairs of one expert.
 //   gate_up  act[pair] = silu(h[row] Wg_e^T) * (h[row] Wu_e^T)      per tile, float accumulation
 //   down     y[pair]   = act[pair] Wd_e^T                           per tile, float results
@@ -62,12 +65,12 @@ __device__ __forceinline__ void route_load(const bf16* p, float (&v)[8]) {
 template <typename T, typename W, int RB>
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_kernel(const T* __restrict__ h, int ldh, const W* __restrict__ wr, int rows, int D, int E, int G, int keep,
-                 int top, float scale, int has_gate, int vec_ok, int* __restrict__ idx, float* __restrict__ wt,
-                 float* __restrict__ gate_out) {
+                 int top, float scale, int has_gate, int vec_ok, int sigmoid_scores, const float* __restrict__ correction,
+                 int group_top, int* __restrict__ idx, float* __restrict__ wt, float* __restrict__ gate_out) {
   extern __shared__ float route_smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int row0 = blockIdx.x * RB;
-  const int zstride = (E + 1 + G + 3) & ~3;                 // per row: scores, the gate's logit, the groups' best
+  const int zstride = (2 * E + 1 + G + 3) & ~3;             // per row: scores, the gate's logit, the groups' scores, choice scores
   float* hs = route_smem + RB * zstride;                    // RB rows of h (16-byte aligned)
   for (int rr = 0; rr < RB; ++rr) {
     const bool live = row0 + rr < rows;
@@ -131,50 +134,64 @@ moe_route_kernel(const T* __restrict__ h, int ldh, const W* __restrict__ wr, int
     if (row >= rows) break;
     float* z = route_smem + rr * zstride;
     float* gb = z + E + 1;
-    float m = -INFINITY;
-    for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
-    m = warp_max(m);
-    float sum = 0.f;
-    for (int e = lane; e < E; e += 32) sum += expf(z[e] - m);
-    sum = warp_sum(sum);
-    __syncwarp();
-    for (int e = lane; e < E; e += 32) z[e] = expf(z[e] - m) / sum;
+    float* ch = gb + G;                                        // choice scores: -inf once taken
+    if (sigmoid_scores) {
+      __syncwarp();
+      for (int e = lane; e < E; e += 32) z[e] = 1.f / (1.f + expf(-z[e]));
+    } else {
+      float m = -INFINITY;
+      for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
+      m = warp_max(m);
+      float sum = 0.f;
+      for (int e = lane; e < E; e += 32) sum += expf(z[e] - m);
+      sum = warp_sum(sum);
+      __syncwarp();
+      for (int e = lane; e < E; e += 32) z[e] = expf(z[e] - m) / sum;
+    }
+    for (int e = lane; e < E; e += 32) ch[e] = z[e] + (correction ? correction[e] : 0.f);
     if (has_gate && lane == 0) gate_out[row] = 1.f / (1.f + expf(-z[E]));
     __syncwarp();
     const int per = E / G;
     const bool limited = G > 1 && keep < G;
     if (limited) {
       for (int g = lane; g < G; g += 32) {
-        float best = 0.f;
-        for (int e = g * per; e < (g + 1) * per; ++e) best = fmaxf(best, z[e]);
-        gb[g] = best;
+        float best = -INFINITY, second = -INFINITY;            // the group's two largest choice scores
+        for (int e = g * per; e < (g + 1) * per; ++e) {
+          const float c = ch[e];
+          if (c > best) { second = best; best = c; }
+          else if (c > second) second = c;
+        }
+        gb[g] = (group_top >= 2 && per >= 2) ? best + second : best;
       }
       __syncwarp();
       for (int k = 0; k < keep; ++k) {
-        float bv = -1.f;
+        float bv = -INFINITY;
         int bi = 0x7fffffff;
-        for (int g = lane; g < G; g += 32)
-          if (gb[g] > bv) { bv = gb[g]; bi = g; }
+        for (int g = lane; g < G; g += 32) {
+          const float c = gb[g];
+          if (c != INFINITY && (bi == 0x7fffffff || c > bv)) { bv = c; bi = g; }
+        }
         warp_argmax(bv, bi);
         __syncwarp();
-        if (lane == 0 && bi < G) gb[bi] = -1.f;               // kept
+        if (lane == 0 && bi < G) gb[bi] = INFINITY;           // kept
         __syncwarp();
       }
     }
     for (int k = 0; k < top; ++k) {
-      float bv = -1.f;
+      float bv = -INFINITY;
       int bi = 0x7fffffff;
       for (int e = lane; e < E; e += 32) {
-        const bool allowed = !limited || gb[e / per] < 0.f;
-        if (allowed && z[e] > bv) { bv = z[e]; bi = e; }
+        const bool allowed = !limited || gb[e / per] == INFINITY;
+        const float c = ch[e];
+        if (allowed && c != -INFINITY && (bi == 0x7fffffff || c > bv)) { bv = c; bi = e; }
       }
       warp_argmax(bv, bi);
       __syncwarp();
       if (lane == 0) {
         const bool ok = bi < E;
         idx[size_t(row) * top + k] = ok ? bi : 0;
-        wt[size_t(row) * top + k] = ok ? bv * scale : 0.f;
-        if (ok) z[bi] = -2.f;                                  // taken
+        wt[size_t(row) * top + k] = ok ? z[bi] * scale : 0.f;
+        if (ok) ch[bi] = -INFINITY;                            // taken
       }
       __syncwarp();
     }
@@ -356,10 +373,12 @@ moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ place_of
 
 template <typename T>
 int launch_moe_route(const void* h, int ldh, const void* wr, int w_f32, int rows, int D, int E, int G, int keep, int top,
-                     float scale, int has_gate, int* idx, float* wt, float* gate_out, cudaStream_t s) {
+                     float scale, int has_gate, int sigmoid_scores, const float* correction, int group_top, int* idx,
+                     float* wt, float* gate_out, cudaStream_t s) {
   if (rows == 0) return 0;
-  if (E < 1 || G < 1 || E % G || keep < 1 || keep > G || top < 1 || top > (E / G) * keep) return KVCM_ERR_UNSUPPORTED;
-  const size_t zstride = (size_t(E + 1 + G) + 3) & ~size_t(3);
+  if (E < 1 || G < 1 || E % G || keep < 1 || keep > G || top < 1 || top > (E / G) * keep || group_top < 1 || group_top > 2)
+    return KVCM_ERR_UNSUPPORTED;
+  const size_t zstride = (size_t(2 * E + 1 + G) + 3) & ~size_t(3);
   int rb = rows >= 512 ? 8 : 1;                                       // many rows: read the router once for 8 of them
   while (rb > 1 && (rb * (zstride + D)) * sizeof(float) > 160 * 1024) rb /= 2;
   const size_t smem = rb * (zstride + D) * sizeof(float);
@@ -371,7 +390,8 @@ int launch_moe_route(const void* h, int ldh, const void* wr, int w_f32, int rows
     if (smem > 48 * 1024)                                                                                             \
       cudaFuncSetAttribute(moe_route_kernel<T, W, RB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
     moe_route_kernel<T, W, RB><<<(rows + RB - 1) / RB, ROUTE_WARPS * 32, smem, s>>>(                                  \
-        (const T*)h, ldh, (const W*)wr, rows, D, E, G, keep, top, scale, has_gate, vec_ok, idx, wt, gate_out);        \
+        (const T*)h, ldh, (const W*)wr, rows, D, E, G, keep, top, scale, has_gate, vec_ok, sigmoid_scores, correction, \
+        group_top, idx, wt, gate_out);                                                                                \
   } while (0)
 #define KVCM_ROUTE_RB(W)                                                                                              \
   do {                                                                                                                \
@@ -462,10 +482,11 @@ KVCM_API int kvcm_moe_experts_tc_bf16(const void* h, int ldh, const void* wgu, c
 
 #define KVCM_MOE(SUFFIX, T)                                                                                          \
   KVCM_API int kvcm_moe_route_##SUFFIX(const void* h, int ldh, const void* wr, int w_f32, int rows, int D, int E,    \
-                                       int G, int keep, int top, float scale, int has_gate, int* idx, float* wt,     \
+                                       int G, int keep, int top, float scale, int has_gate, int sigmoid_scores,      \
+                                       const float* correction, int group_top, int* idx, float* wt,                  \
                                        float* gate_out, void* stream) {                                              \
-    return launch_moe_route<T>(h, ldh, wr, w_f32, rows, D, E, G, keep, top, scale, has_gate, idx, wt, gate_out,      \
-                               (cudaStream_t)stream);                                                                \
+    return launch_moe_route<T>(h, ldh, wr, w_f32, rows, D, E, G, keep, top, scale, has_gate, sigmoid_scores,         \
+                               correction, group_top, idx, wt, gate_out, (cudaStream_t)stream);                      \
   }                                                                                                                  \
   KVCM_API int kvcm_moe_experts_##SUFFIX(const void* h, int ldh, const void* wgu, const void* wd, const int* idx,    \
                                          int rows, int top, int E, int F, int D, int* work, void* act, float* y,     \

@@ -148,7 +148,7 @@ class ModelRunner:
         n = ctx.logit_rows.numel()
         if n == 0:
             return None
-        h_last = torch.empty((n, x.shape[1]), dtype=self.dtype, device=x.device)
+        h_last = torch.empty((n, x.shape[-1]), dtype=self.dtype, device=x.device)      # x: [T, width] or [T, streams, width]
         spec.final_norm.forward(x, pending, h_last, rows=ctx.logit_rows)
         return spec.lm_head.forward(h_last, ctx)
 

@@ -1045,11 +1045,17 @@ def latent_norm_cache(v: torch.Tensor, weight: torch.Tensor, slot_mapping: torch
 # ---------------------------------------------------------------------------- routed experts
 
 def moe_route(h: torch.Tensor, router: torch.Tensor, experts: int, groups: int, keep: int, top: int, scale: float,
-              idx: torch.Tensor, wt: torch.Tensor, gate: Optional[torch.Tensor]) -> None:
-    """Per row: float32 router logits, softmax, group-limited choice of ``top`` experts; ``idx`` int32
-    [T, top], ``wt`` float32 [T, top] = score * scale; ``gate`` float32 [T] = sigmoid of the logit of
-    the router matrix's extra row (row ``experts``)."""
-    _cuda(h, router, idx, wt, gate)
+              idx: torch.Tensor, wt: torch.Tensor, gate: Optional[torch.Tensor], scores: str = "softmax",
+              correction: Optional[torch.Tensor] = None, group_top: int = 1) -> None:
+    """Per row: float32 router logits, scores (``scores``: "softmax" over all experts or "sigmoid" of each
+    logit), group-limited choice of ``top`` experts; ``idx`` int32 [T, top], ``wt`` float32 [T, top] =
+    score * scale; ``gate`` float32 [T] = sigmoid of the logit of the router matrix's extra row (row
+    ``experts``).  ``correction`` (float32 [experts]) is added to the scores for the choice only;
+    ``group_top``: a group's score is the sum of its 1 or 2 largest choice scores."""
+    _cuda(h, router, idx, wt, gate, correction)
+    _need(scores in ("softmax", "sigmoid") and group_top in (1, 2), "moe_route: scores 'softmax' | 'sigmoid', group_top 1 | 2")
+    _need(correction is None or (correction.dtype == torch.float32 and correction.is_contiguous() and correction.numel() == experts),
+          "moe_route: correction float32 [experts]")
     T, D = h.shape
     _need(h.stride(1) == 1 and router.is_contiguous() and router.shape == (experts + (gate is not None), D)
           and router.dtype in (torch.float32, h.dtype), "moe_route: router [experts (+1), width]")
@@ -1058,7 +1064,8 @@ def moe_route(h: torch.Tensor, router: torch.Tensor, experts: int, groups: int, 
     _need(gate is None or (gate.dtype == torch.float32 and gate.numel() >= T), "moe_route: gate float32 [T]")
     fn = getattr(_lib(), "kvcm_moe_route_" + _suffix(h))
     _check(fn(_p(h), h.stride(0), _p(router), int(router.dtype == torch.float32), T, D, experts, groups, keep, top,
-              ctypes.c_float(scale), int(gate is not None), _p(idx), _p(wt), _p(gate), _stream()), "moe_route",
+              ctypes.c_float(scale), int(gate is not None), int(scores == "sigmoid"), _p(correction), int(group_top),
+              _p(idx), _p(wt), _p(gate), _stream()), "moe_route",
            f"(experts={experts}, groups={groups}, keep={keep}, top={top})")
 
 
@@ -1238,35 +1245,38 @@ def attn_prepare(proj: torch.Tensor, bias: Optional[torch.Tensor], wq: Optional[
                  v_keep: Optional[torch.Tensor], v_first: Optional[torch.Tensor], lam: Optional[torch.Tensor],
                  slot_mapping: Optional[torch.Tensor], q_out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                  nh: int, nkv: int, dk: int, dv: int, interleaved: bool = False,
-                 v_inv_freq: Optional[torch.Tensor] = None) -> None:
+                 v_inv_freq: Optional[torch.Tensor] = None, maps: int = 1) -> None:
     """From the float32 q|k|v projection of a step's rows to the attention kernel's inputs: optional bias,
     optional norm over the whole q and k projections (weights wq, wk), rotation of the first ``rot``
     dimensions of every head, optional per-head norm without weights, optional mixing of the values with
     ``v_first`` by ``lam``; q to ``q_out`` [T, nh*HD] and k, v to the rows' page slots, padded with zeros to the
     cache's head size HD (csrc/cuda/attn_prepare.cu).  ``interleaved``: rotary pairs (2i, 2i+1) instead of
-    (i, i + rot/2); ``v_inv_freq`` (float32 [dv/2]): the values too are turned by their position, over all dv."""
+    (i, i + rot/2); ``v_inv_freq`` (float32 [dv/2]): the values too are turned by their position, over all dv.
+    ``maps`` > 1: every q and k head holds that many score maps of ``dk`` elements side by side; ``q_out`` is
+    [T, nh*maps*HD], one padded head per map with the map at its own place, and a key head caches its maps in a row."""
     _cuda(proj, bias, wq, wk, positions, inv_freq, v_keep, v_first, lam, slot_mapping, q_out, k_cache, v_cache, v_inv_freq)
     _need(v_inv_freq is None or (v_inv_freq.dtype == torch.float32 and v_inv_freq.is_contiguous() and v_inv_freq.numel() * 2 == dv),
           "attn_prepare: v_inv_freq float32 [dv/2]")
     T = q_out.shape[0]
     HD, B = k_cache.shape[3], k_cache.shape[2]
-    n = nh * dk + nkv * dk + nkv * dv
+    n = (nh + nkv) * maps * dk + nkv * dv
+    _need(maps >= 1 and (maps == 1 or wq is None), "attn_prepare: several maps go without the whole-projection norm")
     _need(proj.dtype == torch.float32 and proj.stride(1) == 1 and proj.shape[1] >= n and proj.shape[0] >= T, "attn_prepare: proj float32 [T, q|k|v]")
-    for t, m in ((bias, n), (wq, nh * dk), (wk, nkv * dk), (lam, 1)):
+    for t, m in ((bias, n), (wq, nh * maps * dk), (wk, nkv * maps * dk), (lam, 1)):
         _need(t is None or (t.dtype == torch.float32 and t.is_contiguous() and t.numel() == m), "attn_prepare: float32 vectors")
     _need((wq is None) == (wk is None) and (v_first is None) == (lam is None), "attn_prepare: arguments that come in pairs")
     for t in (v_keep, v_first):
         _need(t is None or (t.dtype == torch.float32 and t.is_contiguous() and t.shape == (T, nkv * dv)), "attn_prepare: values float32 [T, nkv*dv]")
-    _need(q_out.is_contiguous() and q_out.shape == (T, nh * HD) and q_out.dtype == k_cache.dtype == v_cache.dtype
+    _need(q_out.is_contiguous() and q_out.shape == (T, nh * maps * HD) and q_out.dtype == k_cache.dtype == v_cache.dtype
           and k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.shape[1] == nkv and v_cache.shape == k_cache.shape
-          and HD >= max(dk, dv), "attn_prepare: outputs")
+          and HD >= max(maps * dk, dv), "attn_prepare: outputs")
     _need(positions.dtype == _I32 and positions.numel() >= T and (slot_mapping is None or (slot_mapping.dtype == _I32 and slot_mapping.numel() >= T)),
           "attn_prepare: positions / slot_mapping int32 [T]")
     _need(inv_freq is None or (inv_freq.dtype == torch.float32 and inv_freq.numel() * 2 == rot), "attn_prepare: inv_freq float32 [rot/2]")
     fn = getattr(_lib(), "kvcm_attn_prepare_" + _suffix(q_out))
     _check(fn(_p(proj), proj.stride(0), _p(bias), _p(wq), _p(wk), _p(positions), _p(inv_freq), int(rot), int(bool(head_norm)),
               ctypes.c_float(eps), _p(v_keep), _p(v_first), _p(lam), _p(slot_mapping), B, _p(q_out), _p(k_cache), _p(v_cache),
-              T, nh, nkv, dk, dv, HD, int(bool(interleaved)), _p(v_inv_freq), _stream()), "attn_prepare", f"(nh={nh}, nkv={nkv}, dk={dk}, dv={dv}, HD={HD})")
+              T, nh, nkv, dk, dv, HD, int(bool(interleaved)), _p(v_inv_freq), int(maps), _stream()), "attn_prepare", f"(nh={nh}, nkv={nkv}, dk={dk}, dv={dv}, HD={HD})")
 
 
 # ------------------------------------------- blocks normalised on both sides, and what comes with them
@@ -1412,3 +1422,73 @@ def latent_q_rope(q: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tens
     fn = getattr(_lib(), "kvcm_latent_q_rope_" + _suffix(qrow))
     _check(fn(_p(q), q.stride(0), _p(positions), _p(inv_freq), 2 * inv_freq.numel(), int(bool(interleaved)), _p(qn_out), _p(qrow),
               T, heads, dn, dr, int(rank), HD, _stream()), "latent_q_rope")
+
+
+# ------------------------------------------- several residual streams, differential and gated attention outputs
+
+def embed_streams(ids: torch.Tensor, table: torch.Tensor, x: torch.Tensor) -> None:
+    """x [T, S, D] float32: every one of the S residual streams of a row starts as the token's row of ``table``."""
+    _cuda(ids, table, x)
+    T, S, D = x.shape
+    _need(x.dtype == torch.float32 and x.is_contiguous() and ids.dtype == _I32 and ids.numel() >= T and table.is_contiguous()
+          and table.shape[1] == D, "embed_streams: x float32 [T, S, D], ids int32 [T], table [vocab, D]")
+    fn = getattr(_lib(), "kvcm_embed_streams_" + _suffix(table))
+    _check(fn(_p(ids), _p(table), _p(x), T, S, D, table.shape[0], _stream()), "embed_streams")
+
+
+def hc_step(x: torch.Tensor, y: Optional[torch.Tensor], bias: Optional[torch.Tensor], mix: Optional[torch.Tensor],
+            out_w: Optional[torch.Tensor], in_w: Optional[torch.Tensor], norm_w: Optional[torch.Tensor], h: Optional[torch.Tensor],
+            eps: float, rows: Optional[torch.Tensor] = None) -> None:
+    """One pass over the residual streams x [T, S, D] (float32, in place).  With ``y`` (float32 [T, D], a sublayer's
+    output; ``bias`` float32 [D] is added to it): x'_t = sum_s mix[s, t] x_s + out_w[t] y for all streams at once.
+    With ``h`` ([n, D], storage dtype): u = sum_s in_w[s] x'_s and h = norm_w * u / sqrt(mean(u^2) + eps).  ``rows``
+    gathers: only rows[i] are worked on and h has one row per index."""
+    _cuda(x, y, bias, mix, out_w, in_w, norm_w, h, rows)
+    T, S, D = x.shape
+    _need(x.dtype == torch.float32 and x.is_contiguous(), "hc_step: x float32 [T, S, D]")
+    _need(y is not None or h is not None, "hc_step: nothing to do")
+    if y is not None:
+        _need(y.dtype == torch.float32 and y.is_contiguous() and y.shape == (T, D) and mix is not None and out_w is not None
+              and mix.dtype == out_w.dtype == torch.float32 and mix.is_contiguous() and mix.shape == (S, S) and out_w.numel() == S
+              and (bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == D)),
+              "hc_step: y float32 [T, D] with mix float32 [S, S], out float32 [S] (bias float32 [D])")
+    n = T
+    if h is not None:
+        _need(in_w is not None and norm_w is not None and in_w.dtype == norm_w.dtype == torch.float32 and in_w.numel() == S
+              and norm_w.is_contiguous() and norm_w.numel() == D and h.is_contiguous() and h.shape[1] == D,
+              "hc_step: h [n, D] with in float32 [S] and the norm's weight float32 [D]")
+    if rows is not None:
+        _need(h is not None and rows.dtype == _I32 and rows.numel() >= h.shape[0], "hc_step: rows int32 [n]")
+        n = h.shape[0]
+    elif h is not None:
+        _need(h.shape[0] == T, "hc_step: h rows != x rows")
+    store = h.dtype if h is not None else torch.float32
+    fn = getattr(_lib(), "kvcm_hc_step_" + _SUFFIX[store])
+    _check(fn(_p(x), _p(y), _p(bias), _p(mix), _p(out_w), _p(in_w) if h is not None else None, _p(norm_w), _p(h), _p(rows), n, S, D,
+              ctypes.c_float(eps), _stream()), "hc_step", f"(streams={S}, hidden={D})")
+
+
+def diff_combine(a: torch.Tensor, gate: Optional[torch.Tensor], lam: torch.Tensor, out: torch.Tensor, heads: int, dv: int,
+                 eps: float, post: float) -> None:
+    """a [T, 2*heads, HD]: the attention outputs of the two maps of every head (heads 2h and 2h+1).  out [T, heads*dv] =
+    (a1 - lam a2) / sqrt(mean_head((a1 - lam a2)^2) + eps) * post * sigmoid(gate[:, h]); ``gate`` float32 [T, >= heads]
+    (a view with a row stride) or None; ``lam`` float32 [1] on the device."""
+    _cuda(a, gate, lam, out)
+    T, H2, HD = a.shape
+    _need(a.is_contiguous() and H2 == 2 * heads and HD >= dv and out.is_contiguous() and out.shape == (T, heads * dv)
+          and out.dtype == a.dtype and lam.dtype == torch.float32 and lam.numel() == 1, "diff_combine: layout")
+    _need(gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape[0] >= T and gate.shape[1] >= heads),
+          "diff_combine: gate float32 [T, heads]")
+    fn = getattr(_lib(), "kvcm_diff_combine_" + _suffix(a))
+    _check(fn(_p(a), _p(gate), gate.stride(0) if gate is not None else 0, _p(lam), _p(out), T, heads, dv, HD, ctypes.c_float(eps),
+              ctypes.c_float(post), _stream()), "diff_combine")
+
+
+def gate_mul(x: torch.Tensor, gate: torch.Tensor, out: torch.Tensor) -> None:
+    """out = x * sigmoid(gate), element by element; x and out [T, n] in the storage dtype, gate float32 [T, n] (row stride free)."""
+    _cuda(x, gate, out)
+    T, n = x.shape
+    _need(x.is_contiguous() and out.is_contiguous() and out.shape == x.shape and out.dtype == x.dtype and gate.dtype == torch.float32
+          and gate.stride(1) == 1 and gate.shape == (T, n), "gate_mul: layout")
+    fn = getattr(_lib(), "kvcm_gate_mul_" + _suffix(x))
+    _check(fn(_p(x), _p(gate), gate.stride(0), _p(out), T, n, _stream()), "gate_mul")

@@ -1,5 +1,5 @@
 """Architectures assembled from parts.  Importing this package registers them."""
 from .spec import ModelSpec, TensorBinding
-from . import bifatar, llama, rivetar, tolanex
+from . import bifatar, llama, lobutar, rivetar, tolanex
 
-__all__ = ["ModelSpec", "TensorBinding", "llama", "tolanex", "bifatar", "rivetar"]
+__all__ = ["ModelSpec", "TensorBinding", "llama", "tolanex", "bifatar", "rivetar", "lobutar"]

@@ -181,3 +181,79 @@ class GeneralAttention(Mixer):
         if self.rotate_values:
             K.rotate_heads(out, ctx.positions, self._v_inv_freq, self.nh, self.hd, bool(getattr(pos, "interleaved", False)), -1.0)
         return matmul_nt(out, self._o_weight, torch.float32, ctx.options)
+
+
+@MIXERS.register("differential_attention")
+class DifferentialAttention(Mixer):
+    """Grouped-query attention whose every head forms TWO softmax maps over the same values and subtracts them:
+
+        q = W_q h + b_q  [heads x 2 x dk],   k = W_k h + b_k  [kv_heads x 2 x dk],   v = W_v h + b_v  [kv_heads x dv]
+        a_m = softmax(scale * rot(q_m) . rot(k_m)) v        for the maps m = 1, 2 (causal; the rotation covers the first
+                                                            ``position.rotary_dim`` elements of each map)
+        lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff     (one number for the layer)
+        o = (a_1 - lambda a_2) / sqrt(mean(o^2) + eps) * (1 - diff)     per head over its dv values, no weight
+        y = W_o concat_heads( sigmoid(w_g,h . h) * o_h ) + b_o           (one gate number per head)
+
+    A key head is cached with its two maps side by side ([k_1 | k_2], 2 dk elements) next to one value head; the
+    attention kernels run 2 x heads query heads, each a padded head that holds one map at its own place and zeros at
+    the other's, so a query meets only its own map of the key and both maps share the value pages.  Cache head size:
+    ``padded_head_dim(max(2 dk, dv))``.  One product gives q | k | v | gate logits (float32 result); bias, rotation
+    and the page write are one kernel, the combination of the maps another.  ``out_bias`` is the output product's
+    bias; a block that adds it itself sets ``defer_bias``."""
+
+    def __init__(self, hidden: int, num_heads: int, num_kv_heads: int, dk: int, dv: int, position: PositionEncoding,
+                 diff: float, scale: Optional[float] = None, norm_eps: float = 1e-6, bias: bool = True, gate: bool = True,
+                 window: int = 0) -> None:
+        super().__init__()
+        if num_kv_heads < 1 or num_heads % num_kv_heads:
+            raise ValueError(f"attention: {num_heads} query heads are not a multiple of {num_kv_heads} KV heads")
+        if getattr(position, "rotary_dim", 0) > dk:
+            raise ValueError("differential_attention: the rotation covers at most one map's size")
+        self.hidden, self.nh, self.nkv, self.dk, self.dv = hidden, num_heads, num_kv_heads, dk, dv
+        self.hd = padded_head_dim(max(2 * dk, dv))
+        self.diff, self.norm_eps, self.window = float(diff), float(norm_eps), int(window or 0)
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(dk)
+        self.has_bias, self.has_gate = bool(bias), bool(gate)
+        self.position = self.add_child("position", position)
+        self.nq, self.nk, self.nv = num_heads * 2 * dk, num_kv_heads * 2 * dk, num_kv_heads * dv
+        self.qkvg = self.add_child("qkvg", Linear(hidden, self.nq + self.nk + self.nv + (num_heads if gate else 0), hidden ** -0.5))
+        self.o = self.add_child("o", Linear(num_heads * dv, hidden, (num_heads * dv) ** -0.5))
+        if self.has_bias:
+            self.declare("bias", (self.nq + self.nk + self.nv,), ("normal", 0.1), "vector")
+            self.declare("o_bias", (hidden,), ("normal", 0.1), "vector")
+        for n in ("lq1", "lk1", "lq2", "lk2"):
+            self.declare(n, (dk,), ("normal", 0.3), "vector")
+        self.defer_bias = False
+        self.out_bias: Optional[torch.Tensor] = None
+        self._bias = self._lambda = None
+
+    def cache_spec(self) -> CacheSpec:
+        return CacheSpec(self.nkv, self.hd, self.window)
+
+    def prepare(self, device, dtype) -> None:
+        super().prepare(device, dtype)
+        f = {n: self.param(n).to(device=device, dtype=torch.float32).reshape(-1).contiguous() for n in self.param_specs()}
+        self._lambda = (torch.exp((f["lq1"] * f["lk1"]).sum()) - torch.exp((f["lq2"] * f["lk2"]).sum()) + self.diff).reshape(1).contiguous()
+        if self.has_bias:
+            self._bias, self.out_bias = f["bias"], f["o_bias"]
+
+    def forward(self, h: torch.Tensor, ctx: StepContext, site: SiteCache) -> torch.Tensor:
+        g = ctx.groups[site.group]
+        pos = self.position
+        T, H = h.shape[0], self.nh
+        proj = self.qkvg.forward(h, ctx, out_dtype=torch.float32)
+        q = torch.empty((T, 2 * H * self.hd), dtype=h.dtype, device=h.device)
+        K.attn_prepare(proj, self._bias, None, None, ctx.positions, pos.inv_freq,
+                       pos.rotary_dim if pos.inv_freq is not None else 0, False, self.norm_eps, None, None, None,
+                       g.slot_mapping if site.writes else None, q, site.k, site.v, H, self.nkv, self.dk, self.dv,
+                       bool(getattr(pos, "interleaved", False)), None, maps=2)
+        maps = torch.empty((T, 2 * H, self.hd), dtype=h.dtype, device=h.device)
+        K.paged_attention(q, maps.view(T, 2 * H * self.hd), site.k, site.v, g.block_tables, ctx, 2 * H, self.nkv, self.hd,
+                          self.scale, self.window)
+        out = torch.empty((T, H * self.dv), dtype=h.dtype, device=h.device)
+        K.diff_combine(maps, proj[:, self.nq + self.nk + self.nv:] if self.has_gate else None, self._lambda, out, H, self.dv,
+                       self.norm_eps, 1.0 - self.diff)
+        y = self.o.forward(out, ctx, out_dtype=torch.float32)
+        if self.out_bias is not None and not self.defer_bias:
+            K.add_bias_rows(y, self.out_bias)
+        return y

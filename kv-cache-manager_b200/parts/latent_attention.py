@@ -103,38 +103,51 @@ class LatentRopeAttention(Mixer):
     behind) and no value pool.  As in ``latent_attention`` the maps W_uk and W_uv move across the softmax: every
     head's query becomes [W_uk^T q_n | rot(q_r) | 0], the engine's paged attention kernels run with all heads
     sharing the pages as keys AND values, and W_uv maps the first ``rank`` elements of a head's output back.
-    Norms, angles and the turn are float32 (the dq|dkv and uq products return float32)."""
+    Norms, angles and the turn are float32 (the dq|dkv and uq products return float32).
+
+    Options: ``q_rank`` = 0: the queries have no latent, q = W_q h comes out of the first product (q | dkv);
+    ``window`` > 0: position i sees j with 0 <= i - j < window (the pages behind the window are given back);
+    ``sink``: a learned number per head whose exponential joins the softmax's denominator; ``gate``: the
+    concatenated heads are multiplied element by element with sigmoid(W_g h), W_g's rows being the last of the
+    first product."""
 
     def __init__(self, hidden: int, heads: int, dn: int, dr: int, dv: int, rank: int, q_rank: int, scale: float,
-                 norm_eps: float, position) -> None:
+                 norm_eps: float, position, window: int = 0, sink: bool = False, gate: bool = False) -> None:
         super().__init__()
         from .attention import padded_head_dim
         if getattr(position, "rotary_dim", 0) > dr:
             raise ValueError("latent_rope_attention: the rotation covers at most the rotated part")
-        self.hidden, self.heads, self.dn, self.dr, self.dv, self.rank, self.q_rank = hidden, heads, dn, dr, dv, rank, q_rank
+        self.hidden, self.heads, self.dn, self.dr, self.dv, self.rank, self.q_rank = hidden, heads, dn, dr, dv, rank, int(q_rank or 0)
         self.scale, self.norm_eps = float(scale), float(norm_eps)
+        self.window, self.has_sink, self.has_gate = int(window or 0), bool(sink), bool(gate)
         self.hd = padded_head_dim(rank + dr)
         self.position = self.add_child("position", position)
         std = hidden ** -0.5
-        self.dq_dkv = self.add_child("dq_dkv", Linear(hidden, q_rank + rank + dr, std))     # one product: dq | dkv
-        self.uq = self.add_child("uq", Linear(q_rank, heads * (dn + dr), q_rank ** -0.5))
+        self.nq = heads * (dn + dr)
+        # one product: (dq, or q itself when the queries have no latent) | dkv | gate logits
+        self.n_first = self.q_rank if self.q_rank else self.nq
+        self.dq_dkv = self.add_child("dq_dkv", Linear(hidden, self.n_first + rank + dr + (heads * dv if gate else 0), std))
+        if self.q_rank:
+            self.uq = self.add_child("uq", Linear(self.q_rank, self.nq, self.q_rank ** -0.5))
+            self.declare("q_norm", (self.q_rank,), ("ones_jitter", 0.1), "vector")
         self.uk = self.add_child("uk", Linear(rank, heads * dn, rank ** -0.5))
         self.uv = self.add_child("uv", Linear(rank, heads * dv, rank ** -0.5))
         self.o = self.add_child("o", Linear(heads * dv, hidden, (heads * dv) ** -0.5))
-        self.declare("q_norm", (q_rank,), ("ones_jitter", 0.1), "vector")
         self.declare("latent_norm", (rank,), ("ones_jitter", 0.1), "vector")
+        if self.has_sink:
+            self.declare("sink", (heads,), ("normal", 1.0), "vector")
         self._uk_t = self._uv = None
         self._f32 = {}
 
     def cache_spec(self) -> CacheSpec:
-        return CacheSpec(1, self.hd, 0, values=False)
+        return CacheSpec(1, self.hd, self.window, values=False)
 
     def prepare(self, device, dtype) -> None:
         super().prepare(device, dtype)
         H, R = self.heads, self.rank
         self._uk_t = self.uk.param("weight").view(H, self.dn, R).transpose(1, 2).contiguous()     # [H, R, dn]
         self._uv = self.uv.param("weight").view(H, self.dv, R)
-        self._f32 = {n: self.param(n).to(device=device, dtype=torch.float32).contiguous() for n in ("q_norm", "latent_norm")}
+        self._f32 = {n: self.param(n).to(device=device, dtype=torch.float32).contiguous() for n in self.param_specs()}
 
     def forward(self, h: torch.Tensor, ctx: StepContext, site: SiteCache) -> torch.Tensor:
         if not site.writes:
@@ -143,10 +156,15 @@ class LatentRopeAttention(Mixer):
         pos = self.position
         M, H, R, HD = h.shape[0], self.heads, self.rank, self.hd
         proj = self.dq_dkv.forward(h, ctx, out_dtype=torch.float32)
-        cq = torch.empty((M, self.q_rank), dtype=h.dtype, device=h.device)
-        K.latent_rope_cache(proj, self._f32["q_norm"], self._f32["latent_norm"], ctx.positions, pos.inv_freq, pos.interleaved,
-                            g.slot_mapping, cq, site.k, self.q_rank, R, self.dr, self.norm_eps)
-        q = self.uq.forward(cq, ctx, out_dtype=torch.float32)
+        if self.q_rank:
+            cq = torch.empty((M, self.q_rank), dtype=h.dtype, device=h.device)
+            K.latent_rope_cache(proj, self._f32["q_norm"], self._f32["latent_norm"], ctx.positions, pos.inv_freq, pos.interleaved,
+                                g.slot_mapping, cq, site.k, self.q_rank, R, self.dr, self.norm_eps)
+            q = self.uq.forward(cq, ctx, out_dtype=torch.float32)
+        else:
+            K.latent_rope_cache(proj[:, self.nq:], None, self._f32["latent_norm"], ctx.positions, pos.inv_freq, pos.interleaved,
+                                g.slot_mapping, None, site.k, 0, R, self.dr, self.norm_eps)
+            q = proj[:, :self.nq]
         qn = torch.empty((M, H, self.dn), dtype=h.dtype, device=h.device)
         qrow = torch.empty((M, H, HD), dtype=h.dtype, device=h.device)
         K.latent_q_rope(q, ctx.positions, pos.inv_freq, pos.interleaved, qn, qrow, H, self.dn, self.dr, R)
@@ -154,6 +172,8 @@ class LatentRopeAttention(Mixer):
         out_lat = torch.empty((M, H, HD), dtype=h.dtype, device=h.device)
         pages = site.k
         K.paged_attention(qrow.view(M, H * HD), out_lat.view(M, H * HD), pages, pages, g.block_tables, ctx, H, 1, HD,
-                          self.scale, 0)
+                          self.scale, self.window, 0.0, self._f32.get("sink"))
         heads_out = per_head_product(out_lat[:, :, :R], self._uv.to(out_lat.dtype), ctx)
+        if self.has_gate:
+            K.gate_mul(heads_out, proj[:, self.n_first + R + self.dr:], heads_out)
         return self.o.forward(heads_out, ctx, out_dtype=torch.float32)
