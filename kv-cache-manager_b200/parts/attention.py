@@ -222,7 +222,7 @@ class DifferentialAttention(Mixer):
             self.declare("bias", (self.nq + self.nk + self.nv,), ("normal", 0.1), "vector")
             self.declare("o_bias", (hidden,), ("normal", 0.1), "vector")
         for n in ("lq1", "lk1", "lq2", "lk2"):
-            self.declare(n, (dk,), ("normal", 0.3), "vector")
+            self.declare(n, (dk,), ("normal", 0.1), "vector")
         self.defer_bias = False
         self.out_bias: Optional[torch.Tensor] = None
         self._bias = self._lambda = None

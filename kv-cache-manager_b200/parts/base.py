@@ -30,7 +30,7 @@ import torch
 
 @dataclass
 class ParamSpec:
-    """One tensor a part owns.  ``init``: ("normal", std) | ("ones",) | ("ones_jitter", std)."""
+    """One tensor a part owns.  ``init``: ("normal", std) | ("ones",) | ("ones_jitter", std) | ("eye_jitter", std)."""
     name: str
     shape: Tuple[int, ...]
     init: Tuple = ("normal", 0.02)

@@ -30,9 +30,9 @@ class HyperConnection(Part):
     def __init__(self, streams: int) -> None:
         super().__init__()
         self.streams = int(streams)
-        self.declare("in", (streams,), ("normal", 0.5), "vector")
-        self.declare("out", (streams,), ("normal", 0.5), "vector")
-        self.declare("mix", (streams, streams), ("normal", 0.5), "vector")
+        self.declare("in", (streams,), ("ones_jitter", 0.3), "vector")
+        self.declare("out", (streams,), ("ones_jitter", 0.3), "vector")
+        self.declare("mix", (streams, streams), ("eye_jitter", 0.2), "vector")
         self.in_w = self.out_w = self.mix_w = None
 
     def prepare(self, device, dtype) -> None:

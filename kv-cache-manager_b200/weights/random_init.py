@@ -1,6 +1,7 @@
 """Random-weights mode: a model folder (config.json + model.safetensors) from a configuration
 and a seed.  Matrices and tables N(0, std) (std from the part's declaration, 0.02 by default),
-norm weights 1, or 1 + N(0, jitter) when asked.  Each tensor's stream is seeded by
+norm weights 1, or 1 + N(0, jitter) when asked; small square matrices that mix
+residual streams I + N(0, jitter).  Each tensor's stream is seeded by
 (seed, tensor name), so values do not depend on the order of generation."""
 from __future__ import annotations
 
@@ -39,6 +40,9 @@ def random_tensors(config, seed: int, dtype: torch.dtype = torch.bfloat16, devic
                 jitter = norm_jitter if init[0] == "ones" else init[1]
                 if jitter:
                     t = t + torch.randn(shape, generator=g, device=device, dtype=torch.float32) * jitter
+            elif init[0] == "eye_jitter":                      # a square matrix around the identity
+                t = torch.eye(shape[0], shape[1], device=device, dtype=torch.float32)
+                t = t + torch.randn(shape, generator=g, device=device, dtype=torch.float32) * init[1]
             else:
                 raise ValueError(f"unknown init {init!r} for {name}")
             yield name, t.to(dtype)

@@ -78,8 +78,9 @@ def mixer_attention(h, m, w: Dict[str, torch.Tensor], eps: float):
     q = (h @ w["q"].T + w["q.b"]).view(T, H, 2, dk)
     k = (h @ w["k"].T + w["k.b"]).view(T, G, 2, dk)
     v = (h @ w["v"].T + w["v.b"]).view(T, G, dv)
-    q = rotate_pairs(q, pos, m["rot"]["base"], m["rot"]["dims"])
-    k = rotate_pairs(k, pos, m["rot"]["base"], m["rot"]["dims"])
+    if m.get("rot"):
+        q = rotate_pairs(q, pos, m["rot"]["base"], m["rot"]["dims"])
+        k = rotate_pairs(k, pos, m["rot"]["base"], m["rot"]["dims"])
     rep = H // G
     kk = k.repeat_interleave(rep, dim=1)                      # head h uses key/value head h // rep
     vv = v.repeat_interleave(rep, dim=1)
