@@ -458,6 +458,73 @@ def rivetar_work(z, T, ctx, decode):
     }
 
 
+# --compare lobutar: the Lobutar design (several residual streams; differential attention; windowed attention over a
+# cached latent with a sink and an output gate; dense feed-forward or routed experts with a shared one; a layer run a
+# second time with the same weights) beside the Llama decoder at equal width, number of layer runs, head count and
+# active feed-forward size.
+LOBUTAR_SIZES = {
+    "h2048": dict(width=2048, streams=4, order=("attention", "latent_attention", "attention", "latent_attention"), shared_run=(2, 0),
+                  heads=16, kv_heads=4, dim=128, map_dim=64, rot_dim=64, kv_rank=192, window=1024, experts=32, moe_top=6,
+                  expert_ff=512, groups=(4, 2), moe_shared=1024, llama_ff=4096),
+    "h4096": dict(width=4096, streams=4, order=("attention", "latent_attention", "latent_attention"), shared_run=(2, 1),
+                  heads=32, kv_heads=8, dim=128, map_dim=64, rot_dim=64, kv_rank=192, window=1024, experts=64, moe_top=6,
+                  expert_ff=1024, groups=(8, 4), moe_shared=2048, llama_ff=8192),
+}
+
+
+def lobutar_configs(z):
+    """(Lobutar config, Llama config) of one size.  Attention layers carry the dense feed-forward, latent layers the
+    experts (chosen plus shared = Llama's inner size); ``shared_run`` = (i, j): layer i runs with layer j's weights.
+    A differential head has two maps of ``map_dim`` and values of ``dim``: its cached key pair is as long as a
+    Llama key.  Llama gets as many layers as Lobutar has layer runs."""
+    from kvcm.config import LlamaConfig, config_from_dict
+    D, H, G, d = z["width"], z["heads"], z["kv_heads"], z["dim"]
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "shared": {"ff": z["moe_shared"]},
+           "router": {"experts": z["experts"], "top": z["moe_top"], "scale": 2.0,
+                      "groups": {"count": z["groups"][0], "keep": z["groups"][1]}}}
+    layers = []
+    for kind in z["order"]:
+        if kind == "attention":
+            m = {"heads": H, "kv_heads": G, "dim": z["map_dim"], "vdim": d, "diff": 0.5, "scale": z["map_dim"] ** -0.5,
+                 "rot": {"base": 10000.0, "dims": z["map_dim"] // 2}}
+            layers.append({"type": kind, "mixer": m, "mlp": {"kind": "dense", "ff": z["llama_ff"]}})
+        else:
+            m = {"heads": H, "dim": d, "rot_dim": z["rot_dim"], "vdim": d, "kv_rank": z["kv_rank"], "scale": (d + z["rot_dim"]) ** -0.5,
+                 "rot": {"base": 10000.0, "dims": z["rot_dim"]}, "mask": {"size": z["window"]}}
+            layers.append({"type": kind, "mixer": m, "mlp": moe})
+    i, j = z["shared_run"]
+    layers[i] = dict(layers[j], weights_of=j)
+    lob = config_from_dict({"architecture": "Lobutar", "vocab": COMPARE_VOCAB, "width": D, "norm": {"eps": 1e-6},
+                            "streams": z["streams"], "layers": layers})
+    lla = LlamaConfig(architecture="LlamaForCausalLM", vocab_size=COMPARE_VOCAB, hidden_size=D, intermediate_size=z["llama_ff"],
+                      num_hidden_layers=len(z["order"]), num_attention_heads=H, num_key_value_heads=G, head_dim=d,
+                      max_position_embeddings=4096, rope_theta=10000.0, rms_norm_eps=1e-6, tie_word_embeddings=False)
+    return lob, lla
+
+
+def lobutar_work(z, T, ctx, decode):
+    """What the families of one Lobutar step have to do at least: flops, or bytes they must move."""
+    D, H, G, d, W, S = z["width"], z["heads"], z["kv_heads"], z["dim"], z["window"], z["streams"]
+    runs = list(z["order"])
+    n_att, n_lat, L = runs.count("attention"), runs.count("latent_attention"), len(runs)
+    seen_all = T * ctx if decode else T * (T + 1) / 2
+    seen_win = T * min(ctx, W) if decode else sum(min(i + 1, W) for i in range(T))
+    lat = z["kv_rank"] + z["rot_dim"]
+    hit = min(z["experts"], T * z["moe_top"])
+    return {
+        # two maps a head: two score products over map_dim and two weighted sums over the values
+        "attention": dict(flops=4.0 * H * ((z["map_dim"] + d) * 2 * seen_all * n_att + lat * seen_win * n_lat),
+                          bytes=2.0 * ((2 * z["map_dim"] + d) * G * T * ctx * n_att + lat * T * min(ctx, W) * n_lat) if decode else None),
+        "moe_experts_tcgen05": dict(flops=2.0 * T * z["moe_top"] * 3 * z["expert_ff"] * D * n_lat,
+                                    bytes=2.0 * hit * 3 * z["expert_ff"] * D * n_lat if decode else None),
+        "feed_forward": dict(flops=2.0 * T * 3 * (z["llama_ff"] * n_att + z["moe_shared"] * n_lat) * D,
+                             bytes=2.0 * 3 * (z["llama_ff"] * n_att + z["moe_shared"] * n_lat) * D if decode else None),
+        # the streams are read and written once per sublayer, the sublayer's output read, its input written
+        "hc_step": dict(flops=None, bytes=T * D * (4.0 * 2 * S + 4.0 + 2.0) * 2 * L),
+        "diff_combine": dict(flops=None, bytes=T * H * d * 2.0 * 3 * n_att),
+    }
+
+
 def compare_main(args) -> int:
     import torch
     from kvcm.config import EngineConfig, KVManagerConfig, SchedulerConfig
@@ -467,6 +534,7 @@ def compare_main(args) -> int:
     first = args.compare
     sizes, configs, first_work = {"bifatar": (BIFATAR_SIZES, bifatar_configs, bifatar_work),
                                   "rivetar": (RIVETAR_SIZES, rivetar_configs, rivetar_work),
+                                  "lobutar": (LOBUTAR_SIZES, lobutar_configs, lobutar_work),
                                   "tolanex": (COMPARE_SIZES, compare_configs, tolanex_work)}[first]
     out = {"compare": f"{first} beside llama at equal width, depth and (active) feed-forward size", "dtype": "bf16",
            "data": "synthetic: random weights, uniform random token ids", "peaks": pk, "sizes": {}}
@@ -478,6 +546,8 @@ def compare_main(args) -> int:
             z = dict(z, layers=len(z["order"]), top=1, ff=z["llama_ff"], shared=0)      # the keys llama_work reads
         elif first == "rivetar":
             z = dict(z, layers=len(rivetar_runs(z)), top=1, ff=z["llama_ff"], shared=0)
+        elif first == "lobutar":
+            z = dict(z, layers=len(z["order"]), top=1, ff=z["llama_ff"], shared=0)
         res = {}
         for arch, cfg in zip((first, "llama"), configs(z)):
             tensors = dict(random_tensors(cfg, 0, torch.bfloat16, device="cuda:0"))
@@ -632,10 +702,10 @@ def main() -> int:
                          "'native' this engine's kernels only, 'library' the library wherever it can stand")
     ap.add_argument("--only", default="all", choices=["all", "prefill"],
                     help="'prefill': run only the 2,048-token prefill step and print its numbers (for profiling)")
-    ap.add_argument("--compare", default="", choices=["", "tolanex", "bifatar", "rivetar"],
-                    help="'tolanex' | 'bifatar' | 'rivetar': instead of the default workload, prefill and decode of that design beside "
+    ap.add_argument("--compare", default="", choices=["", "tolanex", "bifatar", "rivetar", "lobutar"],
+                    help="'tolanex' | 'bifatar' | 'rivetar' | 'lobutar': instead of the default workload, prefill and decode of that design beside "
                          "the Llama decoder at equal sizes, with device time per kernel family")
-    ap.add_argument("--size", default="all", choices=["all"] + sorted(COMPARE_SIZES) + sorted(BIFATAR_SIZES) + sorted(RIVETAR_SIZES),
+    ap.add_argument("--size", default="all", choices=["all"] + sorted(COMPARE_SIZES) + sorted(BIFATAR_SIZES) + sorted(RIVETAR_SIZES) + sorted(LOBUTAR_SIZES),
                     help="with --compare: one size only")
     args = ap.parse_args()
 

@@ -79,12 +79,30 @@ def _rivetar_mini():
             ]}
 
 
+def _lobutar_mini():
+    """A small Lobutar: three residual streams; differential attention with a dense feed-forward, run a second time
+    with the same weights behind a windowed latent layer with grouped experts; a latent layer without a window."""
+    attn = {"heads": 6, "kv_heads": 2, "dim": 32, "vdim": 64, "diff": 0.4, "scale": 0.18, "rot": {"base": 10000.0, "dims": 16}}
+    latent = {"heads": 6, "dim": 48, "rot_dim": 32, "vdim": 64, "kv_rank": 96, "scale": 0.11, "rot": {"base": 100000.0, "dims": 32}}
+    moe = {"kind": "moe", "expert": {"ff": 128}, "shared": {"ff": 256},
+           "router": {"experts": 16, "top": 3, "scale": 1.5, "groups": {"count": 4, "keep": 2}}}
+    first = {"type": "attention", "mixer": attn, "mlp": {"kind": "dense", "ff": 640}}
+    return {"architecture": "Lobutar", "vocab": 1000, "width": 384, "norm": {"eps": 1e-5}, "streams": 3,
+            "layers": [
+                first,
+                {"type": "latent_attention", "mixer": dict(latent, mask={"size": 90}), "mlp": moe},
+                dict(first, weights_of=0),
+                {"type": "latent_attention", "mixer": latent, "mlp": None},
+            ]}
+
+
 PRESETS = {
     # name: (config.json keys, seed, norm jitter); keys with "architecture" go through the registry,
     # the others are those of a Llama dense decoder
     "tolanex-mini": (_tolanex_mini(), 4, 0.1),
     "bifatar-mini": (_bifatar_mini(), 5, 0.1),
     "rivetar-mini": (_rivetar_mini(), 7, 0.1),
+    "lobutar-mini": (_lobutar_mini(), 8, 0.1),
     "tiny-a": (dict(vocab_size=256, hidden_size=64, intermediate_size=172, num_hidden_layers=2,
                     num_attention_heads=4, num_key_value_heads=2, head_dim=16, max_position_embeddings=128,
                     rope_theta=10000.0, rms_norm_eps=1e-5, tie_word_embeddings=False), 0, 0.0),

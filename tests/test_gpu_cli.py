@@ -106,3 +106,16 @@ def test_kvbench_and_kvcorrect_on_the_rivetar_preset():
     rc, out, err = run("kvcorrect", "--preset", "rivetar-mini", "--steps", "8", "--prompts", "3", "--prompt-len", "40")
     assert rc in (0, 2), out[-2000:] + err[-2000:]
     assert "[PASS] alone (scattered pages) = batch" in out and "[PASS] paged = contiguous" in out
+
+
+def test_kvbench_and_kvcorrect_on_the_lobutar_preset():
+    """A fifth architecture through the same flags: several residual streams, a layer run twice with pages of its own,
+    a windowed latent cache and routed experts, served by the scheduler, and kvcorrect's checks."""
+    rc, out, err = run("kvbench", "--preset", "lobutar-mini", "--requests", "10", "--rate", "0", "--prompt-len", "60",
+                       "--output-len", "12", "--max-seq-len", "128", "--num-blocks", "48", "--max-num-seqs", "4",
+                       "--max-batched-tokens", "96", "--warmup", "1")
+    assert rc == 0, err[-2000:]
+    assert "completed 10/10" in out
+    rc, out, err = run("kvcorrect", "--preset", "lobutar-mini", "--steps", "8", "--prompts", "3", "--prompt-len", "40")
+    assert rc in (0, 2), out[-2000:] + err[-2000:]
+    assert "[PASS] alone (scattered pages) = batch" in out and "[PASS] paged = contiguous" in out
