@@ -112,10 +112,13 @@ def main(argv=None) -> int:
         report("paged = contiguous", cont_tokens == batch)
 
         # 4. prefix caching on vs off (not for a model that keeps per-request state: a cached page
-        # would skip tokens whose state is then missing, and the engine refuses the combination)
+        # would skip tokens whose state is then missing; nor for one with several layer groups or a
+        # window, whose pages are not all kept: the engine refuses these combinations)
         from ..cache.pools import plan_cache
-        if plan_cache(spec16).has_state:
-            print("[SKIP] prefix cache on = off (the model keeps per-request state: no prefix caching)")
+        plan = plan_cache(spec16)
+        if plan.has_state or len(plan.groups) != 1 or any(plan.windows):
+            why = "keeps per-request state" if plan.has_state else "has several layer groups or a window"
+            print(f"[SKIP] prefix cache on = off (the model {why}: no prefix caching)")
             print("all checks passed" if ok else "SOME CHECKS FAILED")
             return 0 if ok else 2
         pe = engine(spec16, "bfloat16", prefix=True)

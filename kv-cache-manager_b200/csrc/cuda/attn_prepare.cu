@@ -137,9 +137,20 @@ attn_prepare_kernel(AttnPrepareParams p) {
           store_pair(dst + d, d < p.dk ? x[d] * inv : 0.f, d + 1 < p.dk ? x[d + 1] * inv : 0.f);
       } else {
         const int m = (is_q ? u : u - nqu) % M, lo = m * p.dk;
-        if (is_q) {                                  // the whole padded head: the map at its place, zeros around it
+        if ((p.dk & 1) == 0) {                       // a map starts at an even element: two neighbours a store
+          if (is_q) {                                // the whole padded head: the map at its place, zeros around it
+            for (int d = 2 * lane; d < p.HD; d += 64) {
+              const bool in = d >= lo && d < lo + p.dk;
+              store_pair(dst + d, in ? x[d - lo] * inv : 0.f, in ? x[d - lo + 1] * inv : 0.f);
+            }
+          } else {                                   // this map's part of the key; the last map also the zeros behind
+            for (int d = 2 * lane; d < p.dk; d += 64) store_pair(dst + lo + d, x[d] * inv, x[d + 1] * inv);
+            if (m == M - 1)
+              for (int d = M * p.dk + 2 * lane; d < p.HD; d += 64) store_pair(dst + d, 0.f, 0.f);
+          }
+        } else if (is_q) {
           for (int d = lane; d < p.HD; d += 32) stf(dst + d, d >= lo && d < lo + p.dk ? x[d - lo] * inv : 0.f);
-        } else {                                     // this map's part of the key; the last map also the zeros behind
+        } else {
           for (int d = lane; d < p.dk; d += 32) stf(dst + lo + d, x[d] * inv);
           if (m == M - 1)
             for (int d = M * p.dk + lane; d < p.HD; d += 32) stf(dst + d, 0.f);

@@ -155,8 +155,20 @@ int launch_hc_step(const HcParams& p, int n, cudaStream_t s) {
   return pdl_launch(kernel, dim3(n), dim3(threads), smem, s, p);
 }
 
-// One warp per (row, head).  a: [rows, 2*H heads of HD] (heads 2h and 2h+1 are the two maps of head h).
-template <typename T>
+// One warp per (row, head).  a: [rows, 2*H heads of HD] (heads 2h and 2h+1 are the two maps of head h).  A lane holds
+// two neighbouring elements at a time; heads of up to 512 values stay in registers between the sum of squares and the
+// store (PER pairs a lane), longer ones are read a second time.
+template <typename T> struct Pair;
+template <> struct Pair<float> {
+  static __device__ __forceinline__ float2 load(const float* p) { return *reinterpret_cast<const float2*>(p); }
+  static __device__ __forceinline__ void store(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+};
+template <> struct Pair<bf16> {
+  static __device__ __forceinline__ float2 load(const bf16* p) { return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p)); }
+  static __device__ __forceinline__ void store(bf16* p, float a, float b) { *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b); }
+};
+
+template <typename T, int PER>
 __global__ void __launch_bounds__(256)
 diff_combine_kernel(const T* __restrict__ a, const float* __restrict__ gate, int ldg, const float* __restrict__ lambda,
                     T* __restrict__ out, int rows, int H, int dv, int HD, float eps, float post) {
@@ -169,26 +181,60 @@ diff_combine_kernel(const T* __restrict__ a, const float* __restrict__ gate, int
   const int row = unit / H, h = unit - row * H;
   const T* a1 = a + (size_t(row) * 2 * H + 2 * h) * HD;
   const T* a2 = a1 + HD;
-  float ss = 0.f;
-  for (int d = lane; d < dv; d += 32) {
-    const float o = fmaf(-lam, ldf(a2 + d), ldf(a1 + d));
-    ss = fmaf(o, o, ss);
-  }
-  ss = warp_sum(ss);
-  float f = post / sqrtf(ss / float(dv) + eps);
-  if (gate) f *= 1.f / (1.f + expf(-gate[size_t(row) * ldg + h]));
   T* dst = out + (size_t(row) * H + h) * dv;
-  for (int d = lane; d < dv; d += 32) stf(dst + d, fmaf(-lam, ldf(a2 + d), ldf(a1 + d)) * f);
+  float ss = 0.f;
+  if constexpr (PER > 0) {                            // dv even, dv <= 64 * PER, rows of a and out start at even elements
+    float2 o[PER];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int d = 2 * lane + 64 * i;
+      o[i] = make_float2(0.f, 0.f);
+      if (d < dv) {
+        const float2 x = Pair<T>::load(a1 + d), y = Pair<T>::load(a2 + d);
+        o[i] = make_float2(fmaf(-lam, y.x, x.x), fmaf(-lam, y.y, x.y));
+        ss = fmaf(o[i].x, o[i].x, fmaf(o[i].y, o[i].y, ss));
+      }
+    }
+    ss = warp_sum(ss);
+    float f = post / sqrtf(ss / float(dv) + eps);
+    if (gate) f *= 1.f / (1.f + expf(-gate[size_t(row) * ldg + h]));
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int d = 2 * lane + 64 * i;
+      if (d < dv) Pair<T>::store(dst + d, o[i].x * f, o[i].y * f);
+    }
+  } else {
+    for (int d = lane; d < dv; d += 32) {
+      const float o = fmaf(-lam, ldf(a2 + d), ldf(a1 + d));
+      ss = fmaf(o, o, ss);
+    }
+    ss = warp_sum(ss);
+    float f = post / sqrtf(ss / float(dv) + eps);
+    if (gate) f *= 1.f / (1.f + expf(-gate[size_t(row) * ldg + h]));
+    for (int d = lane; d < dv; d += 32) stf(dst + d, fmaf(-lam, ldf(a2 + d), ldf(a1 + d)) * f);
+  }
 }
 
-template <typename T>
+// out = x * sigmoid(gate): four neighbouring elements a thread where the rows allow 8- and 16-byte accesses.
+template <typename T, int V>
 __global__ void __launch_bounds__(256)
 gate_mul_kernel(const T* __restrict__ x, const float* __restrict__ gate, int ldg, T* __restrict__ out, int n) {
   pdl_launch_dependents();
   pdl_wait();
   const int row = blockIdx.x;
-  for (int i = threadIdx.x; i < n; i += blockDim.x)
-    stf(out + size_t(row) * n + i, ldf(x + size_t(row) * n + i) / (1.f + expf(-gate[size_t(row) * ldg + i])));
+  const T* xr = x + size_t(row) * n;
+  const float* gr = gate + size_t(row) * ldg;
+  T* dst = out + size_t(row) * n;
+  if constexpr (V == 4) {
+    for (int i = 4 * threadIdx.x; i < n; i += 4 * blockDim.x) {
+      const float4 g = *reinterpret_cast<const float4*>(gr + i);
+      const float2 a = Pair<T>::load(xr + i), b = Pair<T>::load(xr + i + 2);
+      Pair<T>::store(dst + i, a.x / (1.f + expf(-g.x)), a.y / (1.f + expf(-g.y)));
+      Pair<T>::store(dst + i + 2, b.x / (1.f + expf(-g.z)), b.y / (1.f + expf(-g.w)));
+    }
+  } else {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) stf(dst + i, ldf(xr + i) / (1.f + expf(-gr[i])));
+  }
 }
 
 }  // namespace kvcm
@@ -231,8 +277,16 @@ static int launch_diff_combine(KVCM_DIFF_COMBINE_ARGS) {
   if (rows == 0) return 0;
   if (H < 1 || dv < 1 || dv > HD) return KVCM_ERR_UNSUPPORTED;
   const int warps = 8, units = rows * H;
-  return pdl_launch(diff_combine_kernel<T>, dim3((units + warps - 1) / warps), dim3(warps * 32), 0, (cudaStream_t)stream,
-                    (const T*)a, gate, ldg, lambda, (T*)out, rows, H, dv, HD, eps, post);
+  const dim3 grid((units + warps - 1) / warps), block(warps * 32);
+  const bool pairs = (dv & 1) == 0 && (HD & 1) == 0 && (reinterpret_cast<uintptr_t>(a) & 7) == 0 && (reinterpret_cast<uintptr_t>(out) & 7) == 0;
+#define KVCM_DIFF(PER)                                                                                                    \
+  return pdl_launch(diff_combine_kernel<T, PER>, grid, block, 0, (cudaStream_t)stream, (const T*)a, gate, ldg, lambda,    \
+                    (T*)out, rows, H, dv, HD, eps, post)
+  if (pairs && dv <= 128) KVCM_DIFF(2);
+  if (pairs && dv <= 256) KVCM_DIFF(4);
+  if (pairs && dv <= 512) KVCM_DIFF(8);
+  KVCM_DIFF(0);
+#undef KVCM_DIFF
 }
 KVCM_API int kvcm_diff_combine_f32(KVCM_DIFF_COMBINE_ARGS) {
   return launch_diff_combine<float>(a, gate, ldg, lambda, out, rows, H, dv, HD, eps, post, stream);
@@ -241,11 +295,18 @@ KVCM_API int kvcm_diff_combine_bf16(KVCM_DIFF_COMBINE_ARGS) {
   return launch_diff_combine<bf16>(a, gate, ldg, lambda, out, rows, H, dv, HD, eps, post, stream);
 }
 
-KVCM_API int kvcm_gate_mul_f32(const void* x, const float* gate, int ldg, void* out, int rows, int n, void* stream) {
+template <typename T>
+static int launch_gate_mul(const void* x, const float* gate, int ldg, void* out, int rows, int n, void* stream) {
   if (rows == 0) return 0;
-  return pdl_launch(gate_mul_kernel<float>, dim3(rows), dim3(256), 0, (cudaStream_t)stream, (const float*)x, gate, ldg, (float*)out, n);
+  const bool vec = (n & 3) == 0 && (ldg & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(gate) & 15) == 0;
+  if (vec)
+    return pdl_launch(gate_mul_kernel<T, 4>, dim3(rows), dim3(256), 0, (cudaStream_t)stream, (const T*)x, gate, ldg, (T*)out, n);
+  return pdl_launch(gate_mul_kernel<T, 1>, dim3(rows), dim3(256), 0, (cudaStream_t)stream, (const T*)x, gate, ldg, (T*)out, n);
+}
+KVCM_API int kvcm_gate_mul_f32(const void* x, const float* gate, int ldg, void* out, int rows, int n, void* stream) {
+  return launch_gate_mul<float>(x, gate, ldg, out, rows, n, stream);
 }
 KVCM_API int kvcm_gate_mul_bf16(const void* x, const float* gate, int ldg, void* out, int rows, int n, void* stream) {
-  if (rows == 0) return 0;
-  return pdl_launch(gate_mul_kernel<bf16>, dim3(rows), dim3(256), 0, (cudaStream_t)stream, (const bf16*)x, gate, ldg, (bf16*)out, n);
+  return launch_gate_mul<bf16>(x, gate, ldg, out, rows, n, stream);
 }
