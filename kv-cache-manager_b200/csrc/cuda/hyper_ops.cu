@@ -52,7 +52,7 @@ struct HcParams {
 };
 
 template <typename T, int V, int MS>   // V columns a thread at a time (4: 16-byte accesses); at most MS streams
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, MS <= 4 ? 4 : 1)
 hc_step_kernel(HcParams p) {
   extern __shared__ __align__(16) float hc_u[];          // D floats: the row's u
   __shared__ float coef[HC_MAX_STREAMS * HC_MAX_STREAMS + 2 * HC_MAX_STREAMS];
@@ -156,8 +156,8 @@ int launch_hc_step(const HcParams& p, int n, cudaStream_t s) {
 }
 
 // One warp per (row, head).  a: [rows, 2*H heads of HD] (heads 2h and 2h+1 are the two maps of head h).  A lane holds
-// two neighbouring elements at a time; heads of up to 512 values stay in registers between the sum of squares and the
-// store (PER pairs a lane), longer ones are read a second time.
+// four neighbouring elements at a time; heads of up to 512 values stay in registers between the sum of squares and the
+// store (PER groups of four a lane), longer or odd ones are read a second time, element by element.
 template <typename T> struct Pair;
 template <> struct Pair<float> {
   static __device__ __forceinline__ float2 load(const float* p) { return *reinterpret_cast<const float2*>(p); }
@@ -166,6 +166,26 @@ template <> struct Pair<float> {
 template <> struct Pair<bf16> {
   static __device__ __forceinline__ float2 load(const bf16* p) { return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p)); }
   static __device__ __forceinline__ void store(bf16* p, float a, float b) { *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b); }
+};
+
+template <typename T> struct Quad;                     // four neighbouring elements as floats
+template <> struct Quad<float> {
+  static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+  static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Quad<bf16> {
+  static __device__ __forceinline__ float4 load(const bf16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+  }
+  static __device__ __forceinline__ void store(bf16* p, float4 v) {
+    uint2 raw;
+    *reinterpret_cast<__nv_bfloat162*>(&raw.x) = __floats2bfloat162_rn(v.x, v.y);
+    *reinterpret_cast<__nv_bfloat162*>(&raw.y) = __floats2bfloat162_rn(v.z, v.w);
+    *reinterpret_cast<uint2*>(p) = raw;
+  }
 };
 
 template <typename T, int PER>
@@ -183,16 +203,16 @@ diff_combine_kernel(const T* __restrict__ a, const float* __restrict__ gate, int
   const T* a2 = a1 + HD;
   T* dst = out + (size_t(row) * H + h) * dv;
   float ss = 0.f;
-  if constexpr (PER > 0) {                            // dv even, dv <= 64 * PER, rows of a and out start at even elements
-    float2 o[PER];
+  if constexpr (PER > 0) {                            // dv a multiple of 4, dv <= 128 * PER, 8- or 16-byte aligned rows
+    float4 o[PER];
 #pragma unroll
     for (int i = 0; i < PER; ++i) {
-      const int d = 2 * lane + 64 * i;
-      o[i] = make_float2(0.f, 0.f);
+      const int d = 4 * lane + 128 * i;
+      o[i] = make_float4(0.f, 0.f, 0.f, 0.f);
       if (d < dv) {
-        const float2 x = Pair<T>::load(a1 + d), y = Pair<T>::load(a2 + d);
-        o[i] = make_float2(fmaf(-lam, y.x, x.x), fmaf(-lam, y.y, x.y));
-        ss = fmaf(o[i].x, o[i].x, fmaf(o[i].y, o[i].y, ss));
+        const float4 x = Quad<T>::load(a1 + d), y = Quad<T>::load(a2 + d);
+        o[i] = make_float4(fmaf(-lam, y.x, x.x), fmaf(-lam, y.y, x.y), fmaf(-lam, y.z, x.z), fmaf(-lam, y.w, x.w));
+        ss = fmaf(o[i].x, o[i].x, fmaf(o[i].y, o[i].y, fmaf(o[i].z, o[i].z, fmaf(o[i].w, o[i].w, ss))));
       }
     }
     ss = warp_sum(ss);
@@ -200,8 +220,8 @@ diff_combine_kernel(const T* __restrict__ a, const float* __restrict__ gate, int
     if (gate) f *= 1.f / (1.f + expf(-gate[size_t(row) * ldg + h]));
 #pragma unroll
     for (int i = 0; i < PER; ++i) {
-      const int d = 2 * lane + 64 * i;
-      if (d < dv) Pair<T>::store(dst + d, o[i].x * f, o[i].y * f);
+      const int d = 4 * lane + 128 * i;
+      if (d < dv) Quad<T>::store(dst + d, make_float4(o[i].x * f, o[i].y * f, o[i].z * f, o[i].w * f));
     }
   } else {
     for (int d = lane; d < dv; d += 32) {
@@ -278,13 +298,13 @@ static int launch_diff_combine(KVCM_DIFF_COMBINE_ARGS) {
   if (H < 1 || dv < 1 || dv > HD) return KVCM_ERR_UNSUPPORTED;
   const int warps = 8, units = rows * H;
   const dim3 grid((units + warps - 1) / warps), block(warps * 32);
-  const bool pairs = (dv & 1) == 0 && (HD & 1) == 0 && (reinterpret_cast<uintptr_t>(a) & 7) == 0 && (reinterpret_cast<uintptr_t>(out) & 7) == 0;
+  const bool pairs = (dv & 3) == 0 && (HD & 3) == 0 && (reinterpret_cast<uintptr_t>(a) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
 #define KVCM_DIFF(PER)                                                                                                    \
   return pdl_launch(diff_combine_kernel<T, PER>, grid, block, 0, (cudaStream_t)stream, (const T*)a, gate, ldg, lambda,    \
                     (T*)out, rows, H, dv, HD, eps, post)
-  if (pairs && dv <= 128) KVCM_DIFF(2);
-  if (pairs && dv <= 256) KVCM_DIFF(4);
-  if (pairs && dv <= 512) KVCM_DIFF(8);
+  if (pairs && dv <= 128) KVCM_DIFF(1);
+  if (pairs && dv <= 256) KVCM_DIFF(2);
+  if (pairs && dv <= 512) KVCM_DIFF(4);
   KVCM_DIFF(0);
 #undef KVCM_DIFF
 }
