@@ -521,7 +521,8 @@ class LobutarConfig(ModelConfig):
     "latent_attention": mixer {heads, dim, rot_dim, vdim, kv_rank, scale, rot {base, dims}, mask {size} (optional)}.
     ``mlp`` is null, {kind: "dense", ff} or {kind: "moe", expert {ff}, router {experts, top, scale, groups {count, keep}},
     shared {ff} (optional)}.  ``weights_of``: j (optional): the layer has no tensors of its own and runs with layer j's
-    (its entry otherwise equals layer j's).  ``layers`` is kept as the parsed JSON after validation; the builder reads
+    parts (its entry otherwise repeats layer j's, whose sizes and constants are the ones used; j may itself name an
+    earlier layer).  ``layers`` is kept as the parsed JSON after validation; the builder reads
     every size from it."""
     vocab: int = 0
     width: int = 0
@@ -556,11 +557,10 @@ class LobutarConfig(ModelConfig):
                 raise ConfigError(f"{lw} must be an object")
             src = layer.get("weights_of")
             if src is not None:
-                if isinstance(src, bool) or not isinstance(src, int) or not (0 <= src < i) or self.layers[src].get("weights_of") is not None:
-                    raise ConfigError(f"{lw}: weights_of must name an earlier layer that has tensors of its own, got {src!r}")
-                ref = self.layers[src]
-                if any(layer.get(k) != ref.get(k) for k in ("type", "mixer", "mlp")):
-                    raise ConfigError(f"{lw}: a layer that runs with layer {src}'s weights must have the same type, mixer and mlp")
+                if isinstance(src, bool) or not isinstance(src, int) or not (0 <= src < i):
+                    raise ConfigError(f"{lw}: weights_of must name an earlier layer, got {src!r}")
+                if layer.get("type") != self.layers[src].get("type"):
+                    raise ConfigError(f"{lw}: a layer that runs with layer {src}'s weights must have the same type")
             kind = layer.get("type")
             m = _section(layer, "mixer", lw)
             mw = lw + " mixer"

@@ -40,7 +40,8 @@ def build_lobutar(cfg: LobutarConfig, norm_init=("ones_jitter", 0.1)) -> ModelSp
     blocks, order, block_of, ignorable = [], [], {}, []
     for i, layer in enumerate(cfg.layers):
         if layer.get("weights_of") is not None:          # another run of an earlier layer's block, with pages of its own
-            order.append(LayerCall(block_of[int(layer["weights_of"])]))
+            block_of[i] = block_of[int(layer["weights_of"])]
+            order.append(LayerCall(block_of[i]))
             continue
         m, p = layer["mixer"], f"l{i}.mix."
         rot = m.get("rot")

@@ -33,8 +33,8 @@ def test_config_is_read_and_written_back():
     (lambda d: d["layers"][1]["mlp"].pop("expert"), "expert"),
     (lambda d: d["layers"][0].__setitem__("mlp", {"kind": "conv"}), "dense"),
     (lambda d: d["layers"][2].__setitem__("weights_of", 2), "weights_of"),
-    (lambda d: d["layers"][4].__setitem__("weights_of", 2), "weights_of"),
-    (lambda d: d["layers"][2]["mixer"].__setitem__("heads", 8), "same type"),
+    (lambda d: d["layers"][4].__setitem__("weights_of", 7), "weights_of"),
+    (lambda d: d["layers"][4].__setitem__("weights_of", 0), "same type"),
     (lambda d: d.__setitem__("streams", 0), "streams"),
     (lambda d: d.pop("norm"), "norm"),
 ])
@@ -69,6 +69,15 @@ def test_builder_names_every_tensor_once_and_runs_shared_layers_twice():
     assert all(plan.site_writes) and len({(g, l) for g, l in zip(plan.site_group, plan.site_layer)}) == 5   # pages of its own per run
     windows = sorted(plan.windows)
     assert windows == [0, 0, 37]
+
+
+def test_a_layer_may_name_a_layer_that_itself_borrows_its_weights():
+    import kvcm
+    from kvcm.engine.model_io import build_spec
+    d = json.loads(json.dumps(LM.CONFIGS["lob-a"]["cfg"]))
+    d["layers"].append(dict(d["layers"][2], weights_of=2))                # layer 5 -> layer 2 -> layer 0
+    spec = build_spec(kvcm.config.config_from_dict(d))
+    assert [c.layer for c in spec.order] == [0, 1, 0, 2, 1, 0] and len(spec.blocks) == 3
 
 
 def test_plain_rotation_and_visibility():
