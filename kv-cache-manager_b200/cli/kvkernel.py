@@ -4,6 +4,7 @@ times decode attention only; here also the decode matrix products).
     kvkernel --family attention --ctx 512,2048 --batch 1,8,64 --block-size 16 --out attn.csv
     kvkernel --family gemm --batch 1,8 --hidden 2048 --ffn 5632 --vocab 32000
     kvkernel --family gemm-large --rows 512,2048
+    kvkernel --family streams --rows 8,2048 --hidden 2048 --streams 4
 
 attention: for every (block size, batch, context): zero-filled K/V/Q, a sequential and a shuffled
 page table, variants paged/contiguous x v1/v2; 5 warm-up runs, ``--iters`` timed runs recorded in
@@ -11,6 +12,9 @@ one CUDA graph and replayed between two events; bytes = 2 * batch * ctx * kv_hea
 (``src/main_kernel_bench.cpp:102``).  "contiguous" is the same kernel on consecutive pages (the
 layout baseline).  gemm: the weight-streaming kernel against the library product for the decode
 shapes of a model of the given sizes, weights rotated so that every call reads cold weights.
+streams: the kernel over several residual streams (write + read + norm, and read + norm alone) beside the plain
+residual add + RMS norm of one stream, and the kernels behind a differential and a gated attention mixer, over
+rotating buffers larger than L2; bytes = what each has to read and write at least.
 Flags: --ctx --batch --block-size (lists), --heads 32 --kv-heads 4 --head-dim 64 --iters 100 --out CSV.
 """
 from __future__ import annotations
@@ -155,6 +159,49 @@ def bench_gemm_large(a, out) -> None:
             raise RuntimeError(f"a bounded wait of the {what} kernel ran out (code {err >> 16}, block {err & 0xffff})")
 
 
+def bench_streams(a, out) -> None:
+    """The stream kernel of hyper-connections beside the one-stream norm, `diff_combine` and `gate_mul`."""
+    import torch
+    from ..engine.peaks import measured_peaks
+    from ..kernels import library as K
+    D, S, rows = a.i32("hidden", 2048), a.i32("streams", 4), a.ints("rows", "8,2048")
+    H, dv = a.i32("heads", 16), a.i32("head-dim", 128)
+    a.warn_unused()
+    dev, bf = "cuda:0", torch.bfloat16
+    peak = measured_peaks()["hbm_gbs"]
+    mix, outw, inw = torch.randn(S, S, device=dev), torch.randn(S, device=dev), torch.randn(S, device=dev)
+    w, bias, lam = torch.randn(D, device=dev), torch.randn(D, device=dev), torch.tensor([0.6], device=dev)
+    if out:
+        out.write("rows,kernel,us,gbs\n")
+    for T in rows:
+        n = max(2, min(16, (1 << 28) // max(1, T * S * D * 4)))          # enough copies to exceed L2
+        xs = [torch.randn(T, S, D, device=dev) for _ in range(n)]
+        ys = [torch.randn(T, D, device=dev) for _ in range(n)]
+        hs = [torch.empty(T, D, dtype=bf, device=dev) for _ in range(n)]
+        x1 = [torch.randn(T, D, device=dev) for _ in range(n)]
+        d1 = [torch.randn(T, D, device=dev).to(bf) for _ in range(n)]
+        maps = [torch.randn(T, 2 * H, dv, device=dev).to(bf) for _ in range(n)]
+        gates = [torch.randn(T, H * dv + H, device=dev) for _ in range(n)]
+        cat = [torch.empty(T, H * dv, dtype=bf, device=dev) for _ in range(n)]
+        wb = w.to(bf)
+        cases = [
+            ("hc_step write+read+norm", T * D * (8.0 * S + 4 + 2),
+             [lambda i=i: K.hc_step(xs[i], ys[i], bias, mix, outw, inw, w, hs[i], 1e-6) for i in range(n)]),
+            ("hc_step read+norm", T * D * (4.0 * S + 2),
+             [lambda i=i: K.hc_step(xs[i], None, None, None, None, inw, w, hs[i], 1e-6) for i in range(n)]),
+            ("rmsnorm + residual (one stream)", T * D * 12.0, [lambda i=i: K.rmsnorm(x1[i], d1[i], wb, hs[i], 1e-6) for i in range(n)]),
+            ("diff_combine", T * H * dv * 6.0,
+             [lambda i=i: K.diff_combine(maps[i], gates[i][:, H * dv:], lam, cat[i], H, dv, 1e-6, 0.5) for i in range(n)]),
+            ("gate_mul", T * H * dv * 8.0, [lambda i=i: K.gate_mul(cat[i], gates[i][:, :H * dv], cat[i]) for i in range(n)]),
+        ]
+        for name, nbytes, fns in cases:
+            us = graph_time_us(fns)
+            gbs = nbytes / us / 1e3
+            print(f"rows={T:<5} {name:<34} {us:8.1f} us {gbs:8.0f} GB/s  {gbs / peak:5.2f} of the copy rate")
+            if out:
+                out.write(f"{T},{name},{us:.3f},{gbs:.1f}\n")
+
+
 def main(argv=None) -> int:
     from .args import Args
     a = Args(argv)
@@ -168,8 +215,10 @@ def main(argv=None) -> int:
             bench_gemm(a, out)
         elif family == "gemm-large":
             bench_gemm_large(a, out)
+        elif family == "streams":
+            bench_streams(a, out)
         else:
-            raise ValueError(f"unknown --family '{family}' (attention | gemm | gemm-large)")
+            raise ValueError(f"unknown --family '{family}' (attention | gemm | gemm-large | streams)")
         if out:
             out.close()
     except Exception as e:

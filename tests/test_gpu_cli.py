@@ -60,6 +60,10 @@ def test_kvkernel_families(tmp_path):
                        "--heads", "4", "--kv-heads", "2", "--head-dim", "64")
     assert rc == 0, err[-2000:]
     assert "gate_up" in out and "lm_head" in out
+    rc, out, err = run("kvkernel", "--family", "streams", "--rows", "4,300", "--hidden", "136", "--streams", "3", "--heads", "3",
+                       "--head-dim", "24")
+    assert rc == 0, err[-2000:]
+    assert "hc_step write+read+norm" in out and "diff_combine" in out
     rc, out, err = run("kvkernel", "--family", "nonsense")
     assert rc != 0
 
